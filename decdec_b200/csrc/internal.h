@@ -1,0 +1,23 @@
+// Internal launch interface between the host-side API (host.cu) and the kernel translation units.
+#pragma once
+#include "common.cuh"
+#include "gemv_bcq.cuh"
+#include "gemv_anyprec.cuh"
+#include "gemv_sqllm.cuh"
+
+namespace dd {
+
+// Each launcher starts ONE grid: blocks [0, d.n_cta) run the compensation role, the rest the GEMV.
+cudaError_t launch_dec_only(int dt, const DecParams& d, const FinParams& f, cudaStream_t s);
+cudaError_t launch_bcq(int dt, const BcqParams& g, const DecParams& d, const FinParams& f, cudaStream_t s);
+cudaError_t launch_anyprec(int dt, const ApParams& g, const DecParams& d, const FinParams& f, cudaStream_t s);
+cudaError_t launch_sqllm(int dt, const SqParams& g, const DecParams& d, const FinParams& f, cudaStream_t s);
+cudaError_t launch_ap_dequant(int dt, const uint32_t* qweight, const void* lut, void* out, uint32_t N, uint32_t K,
+                              uint32_t bits, cudaStream_t s);
+cudaError_t launch_burner(int blocks, long long iters, cudaStream_t s);
+
+size_t dec_only_smem();
+size_t anyprec_smem(uint32_t K, bool fast3);
+size_t sqllm_smem(uint32_t K);
+
+}  // namespace dd

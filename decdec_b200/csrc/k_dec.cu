@@ -1,0 +1,50 @@
+// Compensation-only launch (entry points `dec` and `unfused_dec`) and the SM-occupying busy kernel.
+#include "internal.h"
+#include "dec_role.cuh"
+
+namespace dd {
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads) k_dec_only(const __grid_constant__ DecParams d, const __grid_constant__ FinParams f) {
+    extern __shared__ __align__(16) unsigned char sm[];
+    dec_role<DT>(d, f, blockIdx.x, sm);
+}
+
+size_t dec_only_smem() { return DecSmem::kBytes; }
+
+template <typename K>
+static cudaError_t set_smem(K kernel, size_t bytes) {
+    if (bytes <= 48 * 1024) return cudaSuccess;
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+cudaError_t launch_dec_only(int dt, const DecParams& d, const FinParams& f, cudaStream_t s) {
+    const size_t smem = DecSmem::kBytes;
+    cudaError_t e;
+    switch (dt) {
+        case FP32: if ((e = set_smem(k_dec_only<FP32>, smem))) return e; k_dec_only<FP32><<<d.n_cta, kThreads, smem, s>>>(d, f); break;
+        case FP16: if ((e = set_smem(k_dec_only<FP16>, smem))) return e; k_dec_only<FP16><<<d.n_cta, kThreads, smem, s>>>(d, f); break;
+        default:   if ((e = set_smem(k_dec_only<BF16>, smem))) return e; k_dec_only<BF16><<<d.n_cta, kThreads, smem, s>>>(d, f); break;
+    }
+    return cudaGetLastError();
+}
+
+// Busy kernel: keeps `blocks` CTAs of 1024 threads resident with register-only arithmetic
+// (reference: sm_burner_kernel, decdec.cu:790-823).
+__device__ float g_burner_sink;
+__global__ void __launch_bounds__(1024) k_burner(long long iters) {
+    float a = (float)threadIdx.x, b = 1.0f + 1e-5f * (float)blockIdx.x;
+    for (long long i = 0; i < iters; ++i) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) a = fmaf(a, b, 1e-4f);
+    }
+    if (a == 123.456f) g_burner_sink = a;
+}
+
+cudaError_t launch_burner(int blocks, long long iters, cudaStream_t s) {
+    if (blocks <= 0) return cudaSuccess;
+    k_burner<<<blocks, 1024, 0, s>>>(iters);
+    return cudaGetLastError();
+}
+
+}  // namespace dd

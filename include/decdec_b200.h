@@ -1,0 +1,132 @@
+/*
+ * decdec_b200 - C ABI of the B200 (sm_100a) implementation of the DecDEC decode hot path.
+ *
+ * Every entry point is what a foreign-function binding of the reference's `decdec_ext` module would
+ * bind for that function: plain pointers, sizes, a dtype tag and a CUDA stream; no torch types.
+ * "Reference" below is SNU-ARC/DecDEC; citations are paths inside that repository.
+ *
+ * Conventions
+ *   - all functions return 0 on success, a negative DECDEC_E_* code on failure;
+ *     decdec_last_error() gives the message of the last failure on the calling thread;
+ *   - `dtype` is DECDEC_FP32 / DECDEC_FP16 / DECDEC_BF16 and names the element type of activations,
+ *     outputs, scales, LUTs, alpha and q_bias of that call;
+ *   - a linear layer is y[N] = W[N,K] x[K]; K = in_features, N = out_features;
+ *   - every compute entry point ACCUMULATES into y (y += ...), like the reference kernels;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued, never synchronised;
+ *   - pointers named *_dev must be device-accessible, *_host must be host memory;
+ *   - the library keeps one small fp32 accumulator workspace per (device, stream); the first compute
+ *     call on a stream allocates it and therefore must not happen during stream capture.  Calls that
+ *     share a stream are ordered; calls on different streams use different workspaces.
+ */
+#ifndef DECDEC_B200_H
+#define DECDEC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { DECDEC_FP32 = 0, DECDEC_FP16 = 1, DECDEC_BF16 = 2 };
+
+enum {
+    DECDEC_OK = 0,
+    DECDEC_E_INVALID = -1,      /* bad argument (shape, dtype, alignment, null pointer) */
+    DECDEC_E_UNSUPPORTED = -2,  /* valid in the reference but not implemented here */
+    DECDEC_E_CUDA = -3,         /* a CUDA runtime call failed */
+    DECDEC_E_NOMEM = -4         /* allocation failed */
+};
+
+/* Launch geometry of a config; replaces the dict of read_dec_config (dec_config.cu:337-354). */
+typedef struct decdec_config_info {
+    int32_t num_chunks;            /* ceil(K / 1024) */
+    int32_t chunk_size;            /* 1024 */
+    int32_t k_chunk;               /* channels selected per chunk */
+    int32_t channels_per_tb;       /* packed residual columns (8 outputs each) per DEC thread block */
+    int32_t n_tb;                  /* DEC thread blocks actually launched */
+    int32_t block_dim_x;           /* 256 */
+    int32_t block_dim_y;           /* 1 */
+    int32_t shared_memory_size;    /* dynamic shared memory of a DEC-only launch, bytes */
+    int32_t reduced_shared_memory; /* always 0: the reduced mode of the reference does not exist here */
+} decdec_config_info;
+
+const char* decdec_last_error(void);
+
+/* Version / build probe: returns the compute capability the kernels were compiled for (100). */
+int decdec_compiled_arch(void);
+
+/* ---- context (reference: create_dec_context, dec_context.cu:62-103) ------------------------------
+ * num_tb: thread blocks given to the compensation role.  selected_rows_dev / selected_acts_dev:
+ * caller-owned device buffers of `buffer_size` int32 / dtype elements; after a fused call they hold
+ * the selection, before an unfused call the caller writes the rows there.  The context borrows them. */
+int decdec_create_context(uint32_t num_tb, int32_t* selected_rows_dev, void* selected_acts_dev,
+                          uint32_t buffer_size, int dtype, uintptr_t* out_ctx);
+/* The reference has no destructor for contexts (they leak); this one is an addition. */
+int decdec_destroy_context(uintptr_t ctx);
+
+/* ---- config (reference: create/update/destroy/read_dec_config, dec_config.cu:247-354) -------------
+ * q_residual: int32 [K, N/8] (packed 4-bit residual, cheatsheet.py:99-125).  If q_residual_on_device
+ * is 0 the data is copied into pinned, device-mapped host memory owned by the config and fetched
+ * zero-copy at run time; otherwise the device pointer is used as is (the reference prints a warning).
+ * reordered_scales: dtype [N], layout [nibble][N/8]; copied into device memory owned by the config.
+ * thresholds_host: dtype [K] on the host, BORROWED: entries [0] and [k-1] are read at every launch
+ * (decdec.cu:66-67), so the caller keeps it alive. */
+int decdec_create_config(uintptr_t ctx, uint32_t k_chunk, const int32_t* q_residual, int q_residual_on_device,
+                         uint32_t K, uint32_t N, const void* reordered_scales, int scales_on_device,
+                         const void* thresholds_host, int dtype, uintptr_t* out_cfg);
+int decdec_update_config(uintptr_t cfg, uintptr_t new_ctx, uint32_t k_chunk);
+int decdec_destroy_config(uintptr_t cfg);
+int decdec_read_config(uintptr_t cfg, decdec_config_info* out);
+
+/* ---- compensation alone (reference: dec / unfused_dec, decdec.cu:139-146, :238-245) ---------------
+ * x_dev: dtype [K]; y_dev: dtype [N], accumulated into.  `dec` selects k_chunk channels per 1024
+ * (bucket rule of dec.cu:78-182, ascending channel index inside a bucket) and publishes them in the
+ * context buffers; `unfused_dec` takes the k rows the caller wrote into selected_rows_dev. */
+int decdec_dec(uintptr_t cfg, const void* x_dev, void* y_dev, uint32_t K, uint32_t N, int dtype, void* stream);
+int decdec_unfused_dec(uintptr_t cfg, const void* x_dev, void* y_dev, uint32_t K, uint32_t N, int dtype, void* stream);
+
+/* ---- base GEMVs ------------------------------------------------------------------------------------
+ * anyprec (reference: anyprec_gemv, decdec.cu:324-333): qweight int32 [planes >= bitwidth, N, K/32],
+ *   lut dtype [N, 2^bitwidth]; bitwidth 3..8; fp16/bf16 only.  `planes` is the size of dim 0.
+ * lutgemm (reference: lutgemm_gemv, decdec.cu:485-496): qweight int32 [K/32, bitwidth, N],
+ *   alpha dtype [K/group, bitwidth, N], q_bias dtype [K/group, N]; bitwidth 1..8; N % 8 == 0.
+ * sqllm (reference: sqllm_gemv, decdec.cu:594-603): qweight int32 [K*bitwidth/32, N],
+ *   lut dtype [N, 2^bitwidth]; bitwidth 3 or 4. */
+int decdec_anyprec_gemv(const void* x_dev, void* y_dev, const int32_t* qweight, uint32_t planes, const void* lut,
+                        uint32_t N, uint32_t K, int bitwidth, int dtype, void* stream);
+int decdec_lutgemm_gemv(const void* x_dev, void* y_dev, const int32_t* qweight, const void* alpha, const void* q_bias,
+                        uint32_t N, uint32_t K, int bitwidth, int group_size, int dtype, void* stream);
+int decdec_sqllm_gemv(const void* x_dev, void* y_dev, const int32_t* qweight, const void* lut,
+                      uint32_t N, uint32_t K, int bitwidth, int dtype, void* stream);
+
+/* anyprec_dequant (reference: decdec.cu:386-393): out_dev dtype [N, K] dense weights. */
+int decdec_anyprec_dequant(const int32_t* qweight, const void* lut, void* out_dev,
+                           uint32_t N, uint32_t K, int bitwidth, int dtype, void* stream);
+
+/* ---- fused: base GEMV + compensation in ONE launch (reference: dec_anyprec / dec_lutgemm /
+ * dec_sqllm, decdec.cu:609-779, which fork the GEMV onto a second stream).  The first thread blocks
+ * of the grid run the compensation role, the rest the GEMV; both add into the same fp32
+ * accumulator, rounded once into y. */
+int decdec_dec_anyprec(uintptr_t cfg, const void* x_dev, void* y_dev, const int32_t* qweight, uint32_t planes,
+                       const void* lut, uint32_t N, uint32_t K, int bitwidth, int dtype, void* stream);
+int decdec_dec_lutgemm(uintptr_t cfg, const void* x_dev, void* y_dev, const int32_t* qweight, const void* alpha,
+                       const void* q_bias, uint32_t N, uint32_t K, int bitwidth, int group_size, int dtype, void* stream);
+int decdec_dec_sqllm(uintptr_t cfg, const void* x_dev, void* y_dev, const int32_t* qweight, const void* lut,
+                     uint32_t N, uint32_t K, int bitwidth, int dtype, void* stream);
+
+/* ---- GEMV next to an SM-occupying busy kernel (reference: dummy_anyprec / dummy_lutgemm /
+ * dummy_sqllm, decdec.cu:874-1013): `dummy_sm` blocks of 1024 threads spin for `dummy_iters`
+ * iterations on `stream` while the GEMV runs on a library-owned side stream; joined before return. */
+int decdec_dummy_anyprec(const void* x_dev, void* y_dev, const int32_t* qweight, uint32_t planes, const void* lut,
+                         uint32_t N, uint32_t K, int bitwidth, int dtype, int dummy_sm, long long dummy_iters, void* stream);
+int decdec_dummy_lutgemm(const void* x_dev, void* y_dev, const int32_t* qweight, const void* alpha, const void* q_bias,
+                         uint32_t N, uint32_t K, int bitwidth, int group_size, int dtype, int dummy_sm,
+                         long long dummy_iters, void* stream);
+int decdec_dummy_sqllm(const void* x_dev, void* y_dev, const int32_t* qweight, const void* lut,
+                       uint32_t N, uint32_t K, int bitwidth, int dtype, int dummy_sm, long long dummy_iters, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DECDEC_B200_H */

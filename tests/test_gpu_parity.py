@@ -1,0 +1,438 @@
+"""GPU parity tests: the CUDA library, called through its C ABI (decdec_b200.ops -> capi -> .so),
+against the CPU oracle on the same seeded inputs.
+
+Tolerances (north star): fp16 outputs max abs err <= 1e-2 and rel L2 <= 1e-3 against the float64
+oracle; bf16 outputs carry 8 mantissa bits, so 8e-2 / 6e-3; fp32 1e-3 / 1e-5.  Channel selection is
+compared bit-exactly (rows and recorded activations).
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import forward as ofw
+from oracle import formats, selection
+from tests import problems as P
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"fp16": (1e-2, 1e-3), "bf16": (8e-2, 6e-3), "fp32": (1e-3, 1e-5)}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from decdec_b200 import ops as _ops
+    return _ops
+
+
+def _y0(N, dtype, seed=5):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(1, 1, N, generator=g) * 0.5).to(P.TORCH_DT[dtype])
+
+
+def _assert_close(y, ref, dtype, what=""):
+    ma, rl = P.errors(y, ref)
+    ta, tr = TOL[dtype]
+    assert ma <= ta and rl <= tr, f"{what}: max abs {ma:.3e} (tol {ta}), rel L2 {rl:.3e} (tol {tr})"
+
+
+def _ctx(ops, n_tb, size, dtype):
+    rows = torch.full((size,), -1, dtype=torch.int32, device="cuda")
+    acts = torch.zeros(size, dtype=P.TORCH_DT[dtype], device="cuda")
+    return ops.create_dec_context(n_tb, rows, acts), rows, acts
+
+
+# ------------------------------------------------------------------------------------------------
+# binary-coded (LUT-GEMM) GEMV
+# ------------------------------------------------------------------------------------------------
+
+def test_lutgemm_config0_fp16(ops):
+    """BASELINE config 0: 4096x4096, 3-bit asymmetric group-128, fp16; output accumulated into y0."""
+    N = K = 4096
+    L = P.bcq_layer(N, K, 3, 128, seed=1)
+    x = P.make_activation(K, seed=2)
+    y0 = _y0(N, "fp16")
+    y = y0.clone().cuda()
+    ops.lutgemm_gemv(x.cuda(), y, L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda(), 3, 128)
+    ref = ofw.layer_output(L["w_hat"], P.to_np(x), P.to_np(y0))
+    _assert_close(y, ref, "fp16", "lutgemm config0")
+    # deterministic up to fp32 reduction order: two runs agree to the output rounding
+    y2 = y0.clone().cuda()
+    ops.lutgemm_gemv(x.cuda(), y2, L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda(), 3, 128)
+    assert (y.float() - y2.float()).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16", "fp32"])
+@pytest.mark.parametrize("N,K,bits,group", [
+    (1024, 4096, 3, 128),    # k/v projection
+    (512, 1024, 4, 128),
+    (72, 1088, 3, 32),       # ragged: N not a multiple of 32, K not a multiple of 512, group 32
+    (256, 2048, 1, 64),
+    (128, 1536, 2, 128),
+    (96, 512, 5, 128),
+    (64, 1024, 8, 256),
+])
+def test_lutgemm_shapes(ops, dtype, N, K, bits, group):
+    L = P.random_bcq_layer(N, K, bits, group, seed=N + K + bits, dtype=dtype)
+    x = P.make_activation(K, seed=3, dtype=dtype)
+    y0 = _y0(N, dtype)
+    y = y0.clone().cuda()
+    ops.lutgemm_gemv(x.cuda(), y, L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda(), bits, group)
+    ref = ofw.layer_output(L["w_hat"], P.to_np(x), P.to_np(y0))
+    _assert_close(y, ref, dtype, f"lutgemm {N}x{K} b{bits} g{group} {dtype}")
+
+
+def test_lutgemm_down_proj_fp16(ops):
+    """Llama-3-8B down projection 14336 -> 4096 (28 K slices)."""
+    N, K = 4096, 14336
+    L = P.random_bcq_layer(N, K, 3, 128, seed=11)
+    x = P.make_activation(K, seed=4)
+    y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+    ops.lutgemm_gemv(x.cuda(), y, L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda(), 3, 128)
+    _assert_close(y, ofw.layer_output(L["w_hat"], P.to_np(x)), "fp16", "lutgemm down")
+
+
+# ------------------------------------------------------------------------------------------------
+# selection
+# ------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16", "fp32"])
+@pytest.mark.parametrize("K,k_chunk,n_tb", [
+    (4096, 32, 16), (4096, 8, 4), (4096, 64, 148), (14336, 20, 24), (17920, 16, 32),   # 17920 = 17.5 chunks
+    (1024, 1, 1), (2048, 1000, 8), (1536, 33, 3),
+])
+def test_selection_bit_exact(ops, dtype, K, k_chunk, n_tb):
+    N = 256
+    cs, rs = P.random_residual(N, K, seed=K, dtype=dtype)
+    thr = P.make_thresholds(K, dtype)
+    x = P.make_activation(K, seed=K + k_chunk, dtype=dtype)
+    k = k_chunk * K // 1024
+    ctx, rows, acts = _ctx(ops, n_tb, max(k, 1), dtype)
+    cfg = ops.create_dec_config(ctx, k_chunk, cs, rs, thr)
+    y = torch.zeros(1, 1, N, dtype=P.TORCH_DT[dtype], device="cuda")
+    ops.dec(cfg, x.cuda(), y)
+    torch.cuda.synchronize()
+    exp_rows, exp_acts, _ = P.expected_selection(x, thr, k_chunk, dtype)
+    assert np.array_equal(rows[:k].cpu().numpy(), exp_rows), "selected rows differ from the oracle"
+    assert np.array_equal(P.to_np(acts[:k]), exp_acts), "recorded activations differ"
+    # recorded activation is the signed activation of the recorded row
+    assert np.array_equal(P.to_np(acts[:k]), P.to_np(x).reshape(-1)[exp_rows])
+    delta = ofw.dec_delta(P.to_np(x), exp_rows, cs.numpy(), P.to_np(rs), exp_acts)
+    _assert_close(y, delta, dtype, "dec output")
+    ops.destroy_dec_config(cfg)
+
+
+def test_selection_degenerate_inputs(ops):
+    """all-equal activations, a == b, zeros, and NaN/inf (which belong to no bucket): no trap, oracle-equal."""
+    K, N, k_chunk = 2048, 64, 16
+    cs, rs = P.random_residual(N, K, seed=7)
+    cases = []
+    cases.append((torch.full((K,), 0.5), torch.full((K,), 0.5)))                       # all equal, a == b
+    cases.append((torch.zeros(K), torch.linspace(3, 0.001, K)))                         # all zero input
+    xs = torch.randn(K, generator=torch.Generator().manual_seed(1))
+    xs[5] = float("nan"); xs[1030] = float("inf"); xs[77] = -float("inf")
+    cases.append((xs, torch.sort(torch.randn(K).abs(), descending=True).values))
+    few = torch.full((K,), float("nan")); few[:10] = 1.0                                 # fewer finite values than k
+    cases.append((few, torch.linspace(2, 0.01, K)))
+    for xv, tv in cases:
+        x = xv.half().reshape(1, 1, K)
+        thr = tv.half()
+        ctx, rows, acts = _ctx(ops, 8, 64, "fp16")
+        cfg = ops.create_dec_config(ctx, k_chunk, cs, rs, thr)
+        y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+        ops.dec(cfg, x.cuda(), y)
+        torch.cuda.synchronize()
+        k = k_chunk * K // 1024
+        exp_rows, exp_acts, _ = P.expected_selection(x, thr, k_chunk, "fp16")
+        assert np.array_equal(rows[:k].cpu().numpy(), exp_rows)
+        got = P.to_np(acts[:k])
+        assert np.array_equal(np.nan_to_num(got, nan=123.0), np.nan_to_num(exp_acts, nan=123.0))
+        ops.destroy_dec_config(cfg)
+
+
+def test_dec_reference_smoke_shape(ops):
+    """Shapes and inputs of the reference's own script decdec_extension/tests/test_dec.py
+    (K=14336, N=4096, n_tb=24, k_chunk=20, x~U(-1,1), thresholds = sorted |x|, random int32 residual
+    words including nibble 0), all three dtypes."""
+    K, N, n_tb, k_chunk = 14336, 4096, 24, 20
+    g = torch.Generator().manual_seed(0)
+    q = torch.randint(-2**31, 2**31 - 1, (K, N // 8), dtype=torch.int32, generator=g)
+    scales = torch.rand(N, generator=g)
+    x32 = torch.rand(1, 1, K, generator=g) * 2 - 1
+    thr32 = torch.sort(x32.abs().view(-1), descending=True).values
+    for dtype in ["fp32", "fp16", "bf16"]:
+        td = P.TORCH_DT[dtype]
+        x, thr, sc = x32.to(td), thr32.to(td), scales.to(td)
+        ctx, rows, acts = _ctx(ops, n_tb, K, dtype)
+        cfg = ops.create_dec_config(ctx, k_chunk, q, sc, thr)
+        y = torch.zeros(1, 1, N, dtype=td, device="cuda")
+        ops.dec(cfg, x.cuda(), y)
+        torch.cuda.synchronize()
+        k = k_chunk * K // 1024
+        exp_rows, exp_acts, _ = P.expected_selection(x, thr, k_chunk, dtype)
+        assert np.array_equal(rows[:k].cpu().numpy(), exp_rows)
+        delta = ofw.dec_delta(P.to_np(x), exp_rows, q.numpy(), P.to_np(sc), exp_acts)
+        d = P.to_np(y).reshape(-1) - delta
+        rel = np.linalg.norm(d) / np.linalg.norm(delta)
+        assert rel <= {"fp32": 1e-5, "fp16": 1e-3, "bf16": 6e-3}[dtype], f"{dtype}: rel L2 {rel}"
+        ops.destroy_dec_config(cfg)
+
+
+def test_unfused_dec_exact_topk(ops):
+    """`unfused_dec` with rows written by the caller (exact global top-k, evaltools.py:327-343)."""
+    K, N, k_chunk = 4096, 512, 32
+    cs, rs = P.random_residual(N, K, seed=21)
+    thr = P.make_thresholds(K)
+    x = P.make_activation(K, seed=22)
+    k = k_chunk * K // 1024
+    ctx, rows, acts = _ctx(ops, 16, 32 * 1024, "fp16")
+    cfg = ops.create_dec_config(ctx, k_chunk, cs, rs, thr)
+    top = selection.exact_topk(P.to_np(x).reshape(-1), k)
+    rows[:k] = torch.from_numpy(top).cuda()
+    y0 = _y0(N, "fp16")
+    y = y0.clone().cuda()
+    ops.unfused_dec(cfg, x.cuda(), y)
+    ref = P.to_np(y0).reshape(-1) + ofw.dec_delta(P.to_np(x), top, cs.numpy(), P.to_np(rs))
+    _assert_close(y, ref, "fp16", "unfused_dec")
+
+
+def test_k_chunk_zero_is_noop_and_update(ops):
+    K, N = 2048, 128
+    cs, rs = P.random_residual(N, K, seed=31)
+    thr = P.make_thresholds(K)
+    x = P.make_activation(K, seed=32)
+    ctx, rows, acts = _ctx(ops, 8, 1024, "fp16")
+    cfg = ops.create_dec_config(ctx, 0, cs, rs, thr)
+    y0 = _y0(N, "fp16")
+    y = y0.clone().cuda()
+    ops.dec(cfg, x.cuda(), y)
+    assert torch.equal(y.cpu(), y0)
+    # re-tune without re-uploading the residual (dec_config.cu:295-326)
+    ctx2, rows2, acts2 = _ctx(ops, 3, 1024, "fp16")
+    ops.update_dec_config(cfg, ctx2, 24)
+    info = ops.read_dec_config(cfg)
+    assert info["k_chunk"] == 24 and info["num_chunks"] == 2 and info["chunk_size"] == 1024
+    assert set(info) == {"num_chunks", "chunk_size", "k_chunk", "channels_per_tb", "n_tb", "block_dim_x",
+                         "block_dim_y", "shared_memory_size", "reduced_shared_memory"}
+    ops.dec(cfg, x.cuda(), y)
+    torch.cuda.synchronize()
+    exp_rows, exp_acts, _ = P.expected_selection(x, thr, 24, "fp16")
+    assert np.array_equal(rows2[:48].cpu().numpy(), exp_rows)
+    ref = P.to_np(y0).reshape(-1) + ofw.dec_delta(P.to_np(x), exp_rows, cs.numpy(), P.to_np(rs), exp_acts)
+    _assert_close(y, ref, "fp16", "dec after update")
+    with pytest.raises(RuntimeError, match="buffer size is too small"):
+        ops.update_dec_config(cfg, ctx2, 1000)
+
+
+# ------------------------------------------------------------------------------------------------
+# fused base GEMV + compensation
+# ------------------------------------------------------------------------------------------------
+
+def test_dec_lutgemm_config0(ops):
+    """BASELINE config 0 end to end: real 3-bit quantization, real 4-bit residual, k_chunk = 32."""
+    N = K = 4096
+    L = P.bcq_layer(N, K, 3, 128, seed=1)
+    cs, rs = P.quantized_residual(L["w"], L["w_fake"])
+    thr = P.make_thresholds(K)
+    x = P.make_activation(K, seed=2)
+    ctx, rows, acts = _ctx(ops, 16, 32 * 1024, "fp16")
+    cfg = ops.create_dec_config(ctx, 32, cs, rs, thr)
+    y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+    ops.dec_lutgemm(cfg, x.cuda(), y, L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda(), 3, 128)
+    torch.cuda.synchronize()
+    exp_rows, exp_acts, _ = P.expected_selection(x, thr, 32, "fp16")
+    assert np.array_equal(rows[:128].cpu().numpy(), exp_rows)
+    delta = ofw.dec_delta(P.to_np(x), exp_rows, cs.numpy(), P.to_np(rs), exp_acts)
+    ref = ofw.layer_output(L["w_hat"], P.to_np(x), None, delta)
+    _assert_close(y, ref, "fp16", "dec_lutgemm config0")
+    # the compensation moves the output toward the unquantized layer
+    full = L["w"].astype(np.float64) @ P.to_np(x).reshape(-1)
+    base = ofw.layer_output(L["w_hat"], P.to_np(x))
+    assert np.linalg.norm(P.to_np(y).reshape(-1) - full) < np.linalg.norm(base - full)
+
+
+@pytest.mark.parametrize("k_chunk", [0, 8, 16, 32, 64])
+def test_dec_anyprec_config1_sweep(ops, k_chunk):
+    """BASELINE config 1 (k/v projection shape 4096 -> 1024), 3-bit LUT, k_chunk sweep."""
+    N, K = 1024, 4096
+    L = P.lut_layer(N, K, 3, seed=41)
+    cs, rs = P.random_residual(N, K, seed=42)
+    thr = P.make_thresholds(K)
+    x = P.make_activation(K, seed=43)
+    ctx, rows, acts = _ctx(ops, 16, 32 * 1024, "fp16")
+    cfg = ops.create_dec_config(ctx, k_chunk, cs, rs, thr)
+    y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+    ops.dec_anyprec(cfg, x.cuda(), y, L["qweight"].cuda(), L["lut"].cuda(), 3)
+    exp_rows, exp_acts, _ = P.expected_selection(x, thr, k_chunk, "fp16")
+    delta = ofw.dec_delta(P.to_np(x), exp_rows, cs.numpy(), P.to_np(rs), exp_acts) if k_chunk else None
+    _assert_close(y, ofw.layer_output(L["w_hat"], P.to_np(x), None, delta), "fp16", f"dec_anyprec kc={k_chunk}")
+
+
+@pytest.mark.parametrize("bits", [3, 4])
+def test_dec_sqllm(ops, bits):
+    N, K = 512, 2048
+    L = P.lut_layer(N, K, bits, seed=51, fmt="sqllm")
+    cs, rs = P.random_residual(N, K, seed=52)
+    thr = P.make_thresholds(K)
+    x = P.make_activation(K, seed=53)
+    ctx, rows, acts = _ctx(ops, 6, 1024, "fp16")
+    cfg = ops.create_dec_config(ctx, 16, cs, rs, thr)
+    y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+    ops.dec_sqllm(cfg, x.cuda(), y, L["qweight"].cuda(), L["lut"].cuda(), bits)
+    exp_rows, exp_acts, _ = P.expected_selection(x, thr, 16, "fp16")
+    delta = ofw.dec_delta(P.to_np(x), exp_rows, cs.numpy(), P.to_np(rs), exp_acts)
+    _assert_close(y, ofw.layer_output(L["w_hat"], P.to_np(x), None, delta), "fp16", f"dec_sqllm b{bits}")
+
+
+# ------------------------------------------------------------------------------------------------
+# any-precision and SqueezeLLM GEMVs
+# ------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("N,K,bits", [
+    (4096, 4096, 3),        # q/o projection
+    (1024, 4096, 3),
+    (512, 14336, 3),        # down-projection K
+    (256, 1536, 3),         # tail block (K = 1.5 blocks)
+    (200, 1024 + 128, 3),   # ragged N, small tail
+    (128, 96, 3),           # K below one block and not a multiple of 128 -> generic path
+    (128, 2048, 4),
+    (64, 1056, 5),
+    (64, 1024, 8),
+])
+def test_anyprec_gemv(ops, dtype, N, K, bits):
+    L = P.lut_layer(N, K, bits, seed=N + K + bits, dtype=dtype, real=(bits == 3 and N <= 1024))
+    x = P.make_activation(K, seed=61, dtype=dtype)
+    y0 = _y0(N, dtype)
+    y = y0.clone().cuda()
+    ops.anyprec_gemv(x.cuda(), y, L["qweight"].cuda(), L["lut"].cuda(), bits)
+    ref = ofw.layer_output(L["w_hat"], P.to_np(x), P.to_np(y0))
+    _assert_close(y, ref, dtype, f"anyprec {N}x{K} b{bits} {dtype}")
+
+
+@pytest.mark.parametrize("bits,K", [(3, 4096), (3, 1536), (4, 2048), (8, 1024), (3, 96)])
+def test_anyprec_dequant_exact_and_extra_planes(ops, bits, K):
+    """Dequantized weights equal lut[code] exactly; a tensor with more planes than `bitwidth` is
+    accepted and only the leading planes are used (decdec.cu:295)."""
+    N = 64
+    L = P.lut_layer(N, K, bits, seed=71, real=False)
+    w = ops.anyprec_dequant(L["qweight"].cuda(), L["lut"].cuda(), bits)
+    assert np.array_equal(P.to_np(w), L["w_hat"])
+    if bits < 8:
+        extra = torch.cat([L["qweight"], torch.randint(-2**31, 2**31 - 1, (1, N, K // 32), dtype=torch.int32)], 0)
+        # seed prefix of a wider tensor: the first `bits` planes define the code
+        x = P.make_activation(K, seed=72)
+        y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+        ops.anyprec_gemv(x.cuda(), y, extra.cuda(), L["lut"].cuda(), bits)
+        _assert_close(y, ofw.layer_output(L["w_hat"], P.to_np(x)), "fp16", "anyprec extra planes")
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16", "fp32"])
+@pytest.mark.parametrize("N,K,bits", [(1024, 4096, 3), (512, 4096, 4), (72, 1024, 3), (40, 96, 4)])
+def test_sqllm_gemv(ops, dtype, N, K, bits):
+    L = P.lut_layer(N, K, bits, seed=N + bits, dtype=dtype, fmt="sqllm", real=False)
+    x = P.make_activation(K, seed=81, dtype=dtype)
+    y0 = _y0(N, dtype)
+    y = y0.clone().cuda()
+    ops.sqllm_gemv(x.cuda(), y, L["qweight"].cuda(), L["lut"].cuda(), bits)
+    _assert_close(y, ofw.layer_output(L["w_hat"], P.to_np(x), P.to_np(y0)), dtype, f"sqllm {N}x{K} b{bits}")
+
+
+def test_dummy_entry_points(ops):
+    """GEMV next to the busy kernel gives the same result as the plain GEMV."""
+    N, K = 256, 1024
+    x = P.make_activation(K, seed=91)
+    Lb = P.random_bcq_layer(N, K, 3, 128, seed=92)
+    La = P.lut_layer(N, K, 3, seed=93, real=False)
+    Ls = P.lut_layer(N, K, 4, seed=94, fmt="sqllm", real=False)
+    y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+    ops.dummy_lutgemm(x.cuda(), y, Lb["qweight"].cuda(), Lb["alpha"].cuda(), Lb["q_bias"].cuda(), 3, 128, 8, 1000)
+    _assert_close(y, ofw.layer_output(Lb["w_hat"], P.to_np(x)), "fp16", "dummy_lutgemm")
+    y.zero_()
+    ops.dummy_anyprec(x.cuda(), y, La["qweight"].cuda(), La["lut"].cuda(), 3, 8, 1000)
+    _assert_close(y, ofw.layer_output(La["w_hat"], P.to_np(x)), "fp16", "dummy_anyprec")
+    y.zero_()
+    ops.dummy_sqllm(x.cuda(), y, Ls["qweight"].cuda(), Ls["lut"].cuda(), 4, 8, 1000)
+    _assert_close(y, ofw.layer_output(Ls["w_hat"], P.to_np(x)), "fp16", "dummy_sqllm")
+
+
+# ------------------------------------------------------------------------------------------------
+# API behaviour
+# ------------------------------------------------------------------------------------------------
+
+def test_error_behaviour(ops):
+    N, K = 128, 1024
+    L = P.random_bcq_layer(N, K, 3, 128, seed=1)
+    x = P.make_activation(K, seed=1).cuda()
+    y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+    qw, al, qb = L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda()
+    with pytest.raises(RuntimeError, match="Bitwidth must be between 1 and 8"):
+        ops.lutgemm_gemv(x, y, qw, al, qb, 9, 128)
+    with pytest.raises(RuntimeError, match="Mismatched data types"):
+        ops.lutgemm_gemv(x, y.float(), qw, al, qb, 3, 128)
+    with pytest.raises(RuntimeError, match="must be contiguous"):
+        ops.lutgemm_gemv(x, y, qw.transpose(0, 2), al, qb, 3, 128)
+    with pytest.raises(RuntimeError, match="Batch size must be 1"):
+        ops.lutgemm_gemv(x.expand(2, 1, K).contiguous(), y, qw, al, qb, 3, 128)
+    with pytest.raises(RuntimeError, match="q_weight tensor must be of shape"):
+        ops.lutgemm_gemv(x, y, qw[:, :2].contiguous(), al, qb, 3, 128)
+    La = P.lut_layer(N, K, 3, seed=2, real=False)
+    with pytest.raises(RuntimeError, match="does not support float"):
+        ops.anyprec_gemv(x.float(), y.float(), La["qweight"].cuda(), La["lut"].cuda().float(), 3)
+    with pytest.raises(RuntimeError, match="Bitwidth must be 3 or 4"):
+        ops.sqllm_gemv(x, y, torch.zeros(K * 5 // 32, N, dtype=torch.int32, device="cuda"), torch.zeros(N, 32, dtype=torch.float16, device="cuda"), 5)
+    # context / config coupling
+    rows = torch.zeros(64, dtype=torch.int32, device="cuda")
+    acts = torch.zeros(64, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="must be on GPU"):
+        ops.create_dec_context(4, rows.cpu(), acts)
+    with pytest.raises(RuntimeError, match="same size"):
+        ops.create_dec_context(4, rows[:32], acts)
+    ctx = ops.create_dec_context(4, rows, acts)
+    cs, rs = P.random_residual(N, K, seed=3)
+    thr = P.make_thresholds(K)
+    with pytest.raises(RuntimeError, match="thresholds must be on CPU"):
+        ops.create_dec_config(ctx, 8, cs, rs, thr.cuda())
+    with pytest.raises(RuntimeError, match="same data type"):
+        ops.create_dec_config(ctx, 8, cs, rs.float(), thr)
+    with pytest.raises(RuntimeError, match="Data type mismatch between DECConfig and DECContext"):
+        ops.create_dec_config(ctx, 8, cs, rs.float(), thr.float())
+    with pytest.raises(RuntimeError, match="buffer size is too small"):
+        ops.create_dec_config(ctx, 128, cs, rs, thr)
+    cfg = ops.create_dec_config(ctx, 8, cs, rs, thr)
+    with pytest.raises(RuntimeError, match="Mismatched data types between input tensor and DECConfig"):
+        ops.dec(cfg, x.float(), y.float())
+    with pytest.raises(RuntimeError, match="does not match with DECConfig"):
+        ops.dec(cfg, x[:, :, :512].contiguous(), y)
+    ops.destroy_dec_config(cfg)
+
+
+def test_residual_on_device_and_graph_capture(ops):
+    """q_residual may live on the GPU (reference: warning, no zero-copy); the fused call is
+    capturable in a CUDA graph and replays with new activations."""
+    N, K = 512, 2048
+    L = P.random_bcq_layer(N, K, 3, 128, seed=5)
+    cs, rs = P.random_residual(N, K, seed=6)
+    thr = P.make_thresholds(K)
+    ctx, rows, acts = _ctx(ops, 8, 1024, "fp16")
+    cfg = ops.create_dec_config(ctx, 16, cs.cuda(), rs.cuda(), thr)
+    qw, al, qb = L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda()
+    xbuf = P.make_activation(K, seed=7).cuda()
+    y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        ops.dec_lutgemm(cfg, xbuf, y, qw, al, qb, 3, 128)     # warm-up allocates the stream's workspace
+    torch.cuda.current_stream().wait_stream(s)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        y.zero_()
+        ops.dec_lutgemm(cfg, xbuf, y, qw, al, qb, 3, 128)
+    for seed in (8, 9):
+        x = P.make_activation(K, seed=seed)
+        xbuf.copy_(x.cuda())
+        g.replay()
+        torch.cuda.synchronize()
+        exp_rows, exp_acts, _ = P.expected_selection(x, thr, 16, "fp16")
+        delta = ofw.dec_delta(P.to_np(x), exp_rows, cs.numpy(), P.to_np(rs), exp_acts)
+        _assert_close(y, ofw.layer_output(L["w_hat"], P.to_np(x), None, delta), "fp16", "graph replay")

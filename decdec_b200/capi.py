@@ -12,7 +12,8 @@ from pathlib import Path
 
 FP32, FP16, BF16 = 0, 1, 2
 
-_LIB_PATH = Path(__file__).resolve().parent / "libdecdec_b200.so"
+# DECDEC_B200_LIB selects another build of the same library (e.g. one with debug instrumentation)
+_LIB_PATH = Path(os.environ.get("DECDEC_B200_LIB") or (Path(__file__).resolve().parent / "libdecdec_b200.so"))
 
 
 class DecdecError(RuntimeError):
@@ -35,7 +36,7 @@ def _load():
         raise ImportError(
             f"{_LIB_PATH} is missing: build it with `python -m decdec_b200.build` "
             "(there is no CPU fallback for the decode hot path)")
-    return C.CDLL(str(_LIB_PATH), mode=os.RTLD_GLOBAL if hasattr(os, "RTLD_GLOBAL") else C.DEFAULT_MODE)
+    return C.CDLL(str(_LIB_PATH))
 
 
 lib = _load()

@@ -6,14 +6,31 @@
 //  * a CTA is (row part, column part).  In fused-select mode a row part is a set of 1024-channel
 //    chunks and every CTA of that row part repeats the (cheap) selection of its chunks, so no grid
 //    barrier and no cooperative launch is needed;
-//  * inside a bucket rows are ranked by ascending channel index with warp ballots (the reference
-//    ranks by atomic arrival order, dec.cu:146-154), so the selection is reproducible;
+//  * the bucket that overflows the quota gives its lowest channel indices (the reference takes
+//    whichever rows arrive first at a shared-memory atomic, dec.cu:146-154), and the published order
+//    is reproducible; ranks come from warp ballots and bit-matrix transposes, not atomics;
 //  * residual rows are fetched with 16-byte streaming loads, eight rows in flight per thread;
-//  * the dot products are accumulated in fp32 and scaled once per output.
+//  * the dot products are accumulated in fp32 and scaled once per output; partial sums of the row
+//    groups of a CTA are combined through shared memory without atomics.
 #pragma once
 #include "common.cuh"
 
 namespace dd {
+
+#ifdef DD_PROF
+// debug builds only: per-CTA phase time stamps (ns)
+__device__ unsigned long long g_dd_prof[512 * 8];
+__device__ __forceinline__ void dd_stamp(uint32_t cta, int slot) {
+    if (threadIdx.x == 0 && cta < 512) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g_dd_prof[cta * 8 + slot] = t;
+    }
+}
+#define DD_STAMP(cta, slot) dd_stamp(cta, slot)
+#else
+#define DD_STAMP(cta, slot)
+#endif
 
 // Dynamic shared memory carve-up of the DEC role (bytes).
 struct DecSmem {
@@ -21,11 +38,11 @@ struct DecSmem {
     static constexpr int kBall = kXf + 4096;              // u32    ball[32][32] ballots  [virtual warp][bucket]
     static constexpr int kPre = kBall + 4096;             // u32    pre[32][32]  exclusive counts before a virtual warp
     static constexpr int kFloor = kPre + 4096;            // float  floors[32], ceils[32]
-    static constexpr int kOff = kFloor + 256;             // u32    off[32] + filled
-    static constexpr int kRow = kOff + 256;               // int    srow[1024]
+    static constexpr int kOff = kFloor + 256;             // u32    off[32], filled, totals[32] at +40
+    static constexpr int kRow = kOff + 512;               // int    srow[1024]
     static constexpr int kAct = kRow + 4096;              // float  sact[1024]
-    static constexpr int kRed = kAct + 4096;              // float  red[4096]
-    static constexpr int kFlag = kRed + 16384;            // u32 flag
+    static constexpr int kRed = kAct + 4096;              // float  red[32][257] per-thread partials, [value][thread]
+    static constexpr int kFlag = kRed + 32 * 257 * 4;     // u32 flag
     static constexpr int kBytes = kFlag + 16;
 };
 
@@ -44,15 +61,20 @@ __device__ __forceinline__ float bucket_floor(float a_f, float b_f, int L) {
     return Tr<DT>::to_f(Tr<DT>::from_f(t));
 }
 
-// Select kq rows of chunk `c` into srow/sact (shared).  Returns nothing; all threads participate.
+// Select kq rows of chunk `c` into srow/sact (shared); all threads participate.
+//
+// Rule (same set as the reference, dec.cu:117-177, made reproducible):
+//   bucket(e)  = the lowest L with floor[L] <= |x_e|   (NaN and inf belong to no bucket);
+//   buckets are drained in order 0,1,2,... until kq channels are taken; the bucket that overflows
+//   the quota gives its lowest channel indices.
+// Output order: channels of the fully taken buckets by ascending index, then the picks of the
+// boundary bucket by ascending index.  (The reference order depends on atomic arrival.)
 template <int DT>
 __device__ void dec_select_chunk(const DecParams& p, uint32_t c, uint32_t kq, bool publish, unsigned char* sm) {
     using T = typename Tr<DT>::T;
-    float* xf = reinterpret_cast<float*>(sm + DecSmem::kXf);
-    uint32_t* ball = reinterpret_cast<uint32_t*>(sm + DecSmem::kBall);
-    uint32_t* pre = reinterpret_cast<uint32_t*>(sm + DecSmem::kPre);
     float* floors = reinterpret_cast<float*>(sm + DecSmem::kFloor);
-    uint32_t* off = reinterpret_cast<uint32_t*>(sm + DecSmem::kOff);
+    uint32_t* cum = reinterpret_cast<uint32_t*>(sm + DecSmem::kOff);        // [32] cumulative bucket counts
+    uint32_t* cnt = cum + 32;                                               // [32] per virtual warp (A | B << 16)
     int* srow = reinterpret_cast<int*>(sm + DecSmem::kRow);
     float* sact = reinterpret_cast<float*>(sm + DecSmem::kAct);
 
@@ -61,86 +83,112 @@ __device__ void dec_select_chunk(const DecParams& p, uint32_t c, uint32_t kq, bo
     const uint32_t len = min((uint32_t)kChunk, p.K - s);
     const T* x = reinterpret_cast<const T*>(p.x);
 
-    if (tid < kBuckets) {
-        floors[tid] = bucket_floor<DT>(p.thr_a, p.thr_b, tid);
-    }
     float xv[4];
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
         const uint32_t e = it * kThreads + tid;
-        xv[it] = (e < len) ? Tr<DT>::to_f(x[s + e]) : __int_as_float(0x7fc00000);  // NaN = member of no bucket
-        xf[e] = xv[it];
+        xv[it] = (e < len) ? Tr<DT>::to_f(x[s + e]) : __int_as_float(0x7fc00000);  // NaN = no bucket
     }
-    __syncthreads();
-    if (tid < kBuckets) floors[32 + tid] = (tid == 0) ? __int_as_float(0x7f800000) : floors[tid - 1];
+    if (tid < kBuckets) {
+        floors[tid] = bucket_floor<DT>(p.thr_a, p.thr_b, tid);
+        cum[tid] = 0u;
+    }
     __syncthreads();
 
-    // membership masks (normally one bit; the exact per-bucket test of dec.cu:145 is kept so that
-    // degenerate thresholds behave like the reference)
-    uint32_t mem[4];
+    // G bit L = (|x| >= floor[L]); bucket = lowest set bit
+    uint32_t G[4] = {0u, 0u, 0u, 0u};
+    {
+        float ax[4];
+#pragma unroll
+        for (int it = 0; it < 4; ++it) ax[it] = fabsf(xv[it]);
+        const float4* fl4 = reinterpret_cast<const float4*>(floors);
+#pragma unroll
+        for (int L4 = 0; L4 < 8; ++L4) {
+            const float4 fl = fl4[L4];
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                uint32_t m = (ax[it] >= fl.x) ? 1u : 0u;
+                m |= (ax[it] >= fl.y) ? 2u : 0u;
+                m |= (ax[it] >= fl.z) ? 4u : 0u;
+                m |= (ax[it] >= fl.w) ? 8u : 0u;
+                G[it] |= m << (4 * L4);
+            }
+        }
+    }
+    int bk[4];
+    uint32_t C[4];   // bit L = (bucket <= L)
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
-        const float ax = fabsf(xv[it]);
-        uint32_t m = 0;
-#pragma unroll 8
-        for (int L = 0; L < kBuckets; ++L) {
-            const bool in = (ax >= floors[L]) && (ax < floors[32 + L]);
-            m |= (in ? 1u : 0u) << L;
-        }
-        mem[it] = m;
+        const bool finite = fabsf(xv[it]) < __int_as_float(0x7f800000);   // false for inf and NaN
+        bk[it] = (finite && G[it]) ? (__ffs(G[it]) - 1) : 32;
+        C[it] = (bk[it] < 32) ? (0xffffffffu << bk[it]) : 0u;
     }
-    // ballots: virtual warp vw = it*8 + warp holds elements 32*vw .. 32*vw+31
+    // 32x32 bit transposes: lane L gets, per virtual warp, the ballot of (bucket <= L)
+    uint32_t below = 0;
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
-        const int vw = it * 8 + warp;
-        uint32_t mine = 0;
+        uint32_t v = C[it];
 #pragma unroll
-        for (int L = 0; L < kBuckets; ++L) {
-            const uint32_t b = __ballot_sync(0xffffffffu, (mem[it] >> L) & 1u);
-            if (lane == L) mine = b;
+        for (int d = 16; d >= 1; d >>= 1) {
+            const uint32_t msk = (d == 16) ? 0x0000ffffu : (d == 8) ? 0x00ff00ffu : (d == 4) ? 0x0f0f0f0fu
+                                : (d == 2) ? 0x33333333u : 0x55555555u;
+            const bool up = (lane & d) != 0;
+            const uint32_t send = up ? (v << d) : (v >> d);
+            const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, d);
+            v = up ? ((v & ~msk) | (recv & msk)) : ((v & msk) | (recv & ~msk));
         }
-        ball[vw * 32 + lane] = mine;
+        below += __popc(v);
+    }
+    atomicAdd(&cum[lane], below);
+    __syncthreads();
+
+    // boundary bucket: first L with cum[L] >= kq (32 if the chunk has fewer than kq finite values)
+    const uint32_t cl = cum[lane];
+    const uint32_t ge = __ballot_sync(0xffffffffu, cl >= kq);
+    const int Lb = ge ? (__ffs(ge) - 1) : 32;
+    const uint32_t cprev = (Lb == 0) ? 0u : __shfl_sync(0xffffffffu, cl, (Lb - 1) & 31);
+    const uint32_t total = __shfl_sync(0xffffffffu, cl, 31);
+    const uint32_t quota = (Lb < 32) ? (kq - cprev) : 0u;
+
+    uint32_t balA[4], balB[4];
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        balA[it] = __ballot_sync(0xffffffffu, bk[it] < Lb);
+        balB[it] = __ballot_sync(0xffffffffu, bk[it] == Lb && Lb < 32);
+        if (lane == 0) cnt[it * 8 + warp] = __popc(balA[it]) | (__popc(balB[it]) << 16);
     }
     __syncthreads();
-    if (warp == 0) {
-        // lane = bucket: exclusive prefix over virtual warps, then exclusive scan over buckets
-        uint32_t run = 0;
-        for (int vw = 0; vw < 32; ++vw) {
-            pre[vw * 32 + lane] = run;
-            run += __popc(ball[vw * 32 + lane]);
-        }
-        uint32_t inc = run;
+    uint32_t inc = cnt[lane];
+    const uint32_t own = inc;
 #pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const uint32_t o = __shfl_up_sync(0xffffffffu, inc, d);
-            if (lane >= d) inc += o;
-        }
-        off[lane] = inc - run;
-        if (lane == 31) off[32] = min(inc, kq);  // number of slots that get a real row
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t o = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += o;
     }
-    __syncthreads();
+    const uint32_t excl = inc - own;   // packed exclusive prefix for virtual warp = lane
     const uint32_t lt = (1u << lane) - 1u;
     int* g_rows = p.sel_rows + (size_t)c * p.k_chunk;
     T* g_acts = reinterpret_cast<T*>(p.sel_acts) + (size_t)c * p.k_chunk;
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
-        const int vw = it * 8 + warp;
-        uint32_t m = mem[it];
-        while (m) {
-            const int L = __ffs(m) - 1;
-            m &= m - 1;
-            const uint32_t r = off[L] + pre[vw * 32 + L] + __popc(ball[vw * 32 + L] & lt);
-            if (r < kq) {
-                const int row = (int)(s + it * kThreads + tid);
-                srow[r] = row;
-                sact[r] = xv[it];
-                if (publish) { g_rows[r] = row; g_acts[r] = Tr<DT>::from_f(xv[it]); }
-            }
+        const uint32_t pre = __shfl_sync(0xffffffffu, excl, it * 8 + warp);
+        uint32_t r = 0xffffffffu;
+        if (bk[it] < Lb) {
+            r = (pre & 0xffffu) + __popc(balA[it] & lt);
+        } else if (bk[it] == Lb && Lb < 32) {
+            const uint32_t rb = (pre >> 16) + __popc(balB[it] & lt);
+            if (rb < quota) r = cprev + rb;
+        }
+        if (r < kq) {
+            const int row = (int)(s + it * kThreads + tid);
+            srow[r] = row;
+            sact[r] = xv[it];
+            if (publish) { g_rows[r] = row; g_acts[r] = Tr<DT>::from_f(xv[it]); }
         }
     }
-    // fewer than kq finite members (NaN/inf activations): pad with a harmless (row, 0) pair.
+    // fewer than kq finite values (NaN/inf activations): pad with a harmless (row, 0) pair.
     // The reference aborts with a device assert here (dec.cu:178).
-    const uint32_t filled = off[32];
+    const uint32_t filled = min(total, kq);
     for (uint32_t r = filled + tid; r < kq; r += kThreads) {
         srow[r] = (int)s;
         sact[r] = 0.0f;
@@ -176,13 +224,11 @@ __device__ void dec_fetch(const DecParams& p, float* acc_g, uint32_t nrows, uint
         const uint32_t nw = min(kBlockWords, w1 - cb);
         const uint32_t tv = (nw + VW - 1) / VW;
         const uint32_t R = kThreads / tv;
-        for (uint32_t o = tid; o < nw * 8; o += kThreads) red[o] = 0.0f;
-        __syncthreads();
         const uint32_t v = tid % tv, rg = tid / tv;
-        if (rg < R) {
-            float a[VW * 8];
+        float a[VW * 8];
 #pragma unroll
-            for (int i = 0; i < VW * 8; ++i) a[i] = 0.0f;
+        for (int i = 0; i < VW * 8; ++i) a[i] = 0.0f;
+        if (rg < R) {
             const uint32_t col = cb + v * VW;
             for (uint32_t i0 = rg; i0 < nrows; i0 += R * UN) {
                 if constexpr (VW == 4) {
@@ -224,14 +270,19 @@ __device__ void dec_fetch(const DecParams& p, float* acc_g, uint32_t nrows, uint
                     for (int b = 0; b < UN; ++b) dec_decode_word(q[b], xa[b], a);
                 }
             }
-#pragma unroll
-            for (int i = 0; i < VW * 8; ++i) atomicAdd(&red[v * VW * 8 + i], a[i]);
         }
+        // per-thread partials -> red[value][thread] (pitch 257: conflict-free both ways), then each
+        // output sums its R row groups
+#pragma unroll
+        for (int i = 0; i < VW * 8; ++i) red[i * 257 + tid] = a[i];
         __syncthreads();
         for (uint32_t o = tid; o < nw * 8; o += kThreads) {
+            const uint32_t vv = o / (VW * 8), i = o % (VW * 8);
+            float sum = 0.0f;
+            for (uint32_t r = 0; r < R; ++r) sum += red[i * 257 + r * tv + vv];
             const uint32_t n = cb * 8 + o;
             const float sc = Tr<DT>::to_f(scales[(size_t)(n & 7u) * wpr + (n >> 3)]);
-            atomicAdd(&acc_g[n], red[o] * sc);
+            atomicAdd(&acc_g[n], sum * sc);
         }
         __syncthreads();
     }
@@ -252,6 +303,7 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
     const bool vec = (p.N % 32u) == 0u;
     int* srow = reinterpret_cast<int*>(sm + DecSmem::kRow);
     float* sact = reinterpret_cast<float*>(sm + DecSmem::kAct);
+    DD_STAMP(cta, 0);
 
     if (p.fused_select) {
         const uint32_t num_chunks = (p.K + kChunk - 1) / kChunk;
@@ -260,6 +312,7 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
             const uint32_t kq = p.k_chunk * len / kChunk;
             if (kq == 0) continue;
             dec_select_chunk<DT>(p, c, kq, cp == 0, sm);
+            DD_STAMP(cta, 1);
             if (w1 > w0) {
                 if (vec) dec_fetch<DT, 4>(p, f.acc, kq, w0, w1, sm);
                 else dec_fetch<DT, 1>(p, f.acc, kq, w0, w1, sm);
@@ -285,7 +338,9 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
             }
         }
     }
+    DD_STAMP(cta, 2);
     arrive_and_finalize<DT>(f, t0, t1, reinterpret_cast<unsigned*>(sm + DecSmem::kFlag));
+    DD_STAMP(cta, 3);
 }
 
 }  // namespace dd

@@ -13,8 +13,9 @@ Pinning status: the reference ships no golden vectors and no assertions for this
   * a numpy emulation of the reference CUDA bit manipulation for the any-precision layout
     (`decdec_extension/anyprec.cu:11-66,261-331`).
 The bucket selection of `decdec_extension/dec.cu:78-182` has no CPU counterpart in the reference;
-it is restated here with a canonical (ascending channel index) order inside each bucket, because
-the reference order inside a bucket depends on atomic arrival order.
+it is restated here with a reproducible choice inside the bucket that overflows the quota (lowest
+channel indices first) and a fixed output order, because the reference leaves both to atomic arrival
+order.
 """
 
 from . import formats, residual, selection, forward  # noqa: F401

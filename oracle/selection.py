@@ -2,8 +2,9 @@
 
 Test infrastructure only.  The reference has no CPU implementation of this step; this file restates
 the CUDA kernel's arithmetic exactly (including the mixed half/float recipe of the bucket bounds)
-and fixes the one thing the kernel leaves to chance: inside a bucket the reference appends rows in
-atomic-arrival order (`dec.cu:146-154`), here rows are taken in ascending channel index.
+and fixes what the kernel leaves to chance: the reference appends rows to a bucket in atomic-arrival
+order (`dec.cu:146-154`), so which members of the overflowing bucket are taken, and the order of the
+published rows, vary from run to run; here the lowest channel indices are taken and the order is fixed.
 """
 from __future__ import annotations
 
@@ -64,21 +65,29 @@ def select(x: np.ndarray, a: float, b: float, k_chunk: int, dtype: str = "fp16")
 
     x: [K] values of the activation dtype (any float array holding them exactly).
     Returns (rows int32 [k], acts float64 [k], hist int64 [num_chunks, 32]) where
-    k = k_chunk*K // 1024 (`dec.cu:48`), rows[c*k_chunk + i] is the i-th pick of chunk c
-    (`dec.cu:169-170`), and hist[c, L] is the membership count of bucket L in chunk c.
+    k = k_chunk*K // 1024 (`dec.cu:48`), the picks of chunk c sit at rows[c*k_chunk : c*k_chunk+kq]
+    (`dec.cu:169-170`), and hist[c, L] is the population of bucket L in chunk c.
 
-    Per chunk c of length len <= 1024: kq = k_chunk*len // 1024 (`dec.cu:84-86`); bucket L holds the
+    Per chunk c of length len <= 1024: kq = k_chunk*len // 1024 (`dec.cu:84-86`).  Bucket L holds the
     channels with floor[L] <= |x| < ceil[L], ceil[0] = +inf, ceil[L] = floor[L-1]
-    (`dec.cu:133-137,145`); buckets are drained in order 0,1,2,... until kq rows are taken
-    (`dec.cu:161-177`).  NaN and inf fall in no bucket.  If the buckets hold fewer than kq finite
-    channels the reference trips a device assert (`dec.cu:178`); the oracle (and the CUDA library)
-    instead pad with (first channel of the chunk, activation 0).
+    (`dec.cu:133-137,145`); for floors that do not increase with L this is the LOWEST L with
+    floor[L] <= |x|, which is how the bucket is computed here (NaN and inf fall in no bucket).
+    Buckets are drained in order 0,1,2,... until kq rows are taken (`dec.cu:161-177`).
+
+    What the reference leaves to chance, and this oracle fixes:
+      * which members of the bucket that overflows the quota are taken (reference: atomic arrival
+        order, `dec.cu:146-154`; here: the lowest channel indices);
+      * the order of the published rows (here: members of the fully taken buckets by ascending
+        channel index, then the picks of the overflowing bucket by ascending channel index).
+    Degenerate thresholds (floor[16] > floor[15], which needs thresholds[0] > ~1000*thresholds[k-1]
+    in fp16) could make the reference count one channel in two buckets; here it is in the lower one.
+    If a chunk has fewer than kq finite channels the reference trips a device assert (`dec.cu:178`);
+    the oracle (and the CUDA library) pad with (first channel of the chunk, activation 0).
     """
     x = np.asarray(x, np.float64).reshape(-1)
     K = x.shape[0]
     k_total = k_chunk * K // CHUNK
     floors = bucket_floors(a, b, dtype)
-    ceils = np.concatenate([[np.inf], floors[:-1]])
     num_chunks = (K + CHUNK - 1) // CHUNK
     rows = np.zeros(k_total, np.int32)
     acts = np.zeros(k_total, np.float64)
@@ -87,18 +96,20 @@ def select(x: np.ndarray, a: float, b: float, k_chunk: int, dtype: str = "fp16")
         s, e = c * CHUNK, min((c + 1) * CHUNK, K)
         kq = k_chunk * (e - s) // CHUNK
         ax = np.abs(x[s:e])
-        taken = []
-        for L in range(NUM_BUCKETS):
-            with np.errstate(invalid="ignore"):
-                mem = np.nonzero((ax >= floors[L]) & (ax < ceils[L]))[0]
-            hist[c, L] = mem.size
-            room = kq - len(taken)
-            if room > 0:
-                taken.extend((s + mem[:room]).tolist())
+        with np.errstate(invalid="ignore"):
+            ge = ax[:, None] >= floors[None, :]                      # [len, 32]
+        bucket = np.where(ge.any(1) & np.isfinite(ax), ge.argmax(1), NUM_BUCKETS)
+        hist[c] = np.bincount(bucket, minlength=NUM_BUCKETS + 1)[:NUM_BUCKETS]
+        cum = np.cumsum(hist[c])
+        over = np.nonzero(cum >= kq)[0]
+        lb = int(over[0]) if over.size else NUM_BUCKETS
+        full = np.nonzero(bucket < lb)[0]                            # ascending index
+        taken = list(s + full)
+        if lb < NUM_BUCKETS:
+            quota = kq - len(taken)
+            taken.extend((s + np.nonzero(bucket == lb)[0][:quota]).tolist())
         for i in range(kq):
             pos = c * k_chunk + i
-            if pos >= k_total:
-                break
             if i < len(taken):
                 rows[pos] = taken[i]
                 acts[pos] = x[taken[i]]

@@ -46,6 +46,7 @@ template <> struct Tr<BF16> {
 struct FinParams {
     float* acc;            // [>= N] fp32, all zero between launches
     unsigned* tickets;     // [>= n_tiles], all zero between launches
+    unsigned* err;         // device error word of the workspace (0 = fine)
     void* y;               // caller's output [N], accumulated into
     uint32_t N;
     uint32_t tile_units;   // outputs per tile = 32 * tile_units
@@ -82,10 +83,19 @@ __device__ __forceinline__ uint32_t ldg_stream(const uint32_t* p) {
     return v;
 }
 
+// explicit shared-window load (the table lookups must not degrade to generic loads)
+__device__ __forceinline__ float lds_f32(uint32_t saddr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(saddr));
+    return v;
+}
+
 // Arrive on tiles [t0, t1); the last arriver of a tile folds the accumulator into y.
 // Must be called by all threads of the CTA, after all its reductions into `acc` were issued.
+// `nthreads` = number of threads of the CTA that take part (threads beyond it must have exited).
 template <int DT>
-__device__ __forceinline__ void arrive_and_finalize(const FinParams& f, uint32_t t0, uint32_t t1, unsigned* s_flag) {
+__device__ __forceinline__ void arrive_and_finalize(const FinParams& f, uint32_t t0, uint32_t t1, unsigned* s_flag,
+                                                    uint32_t nthreads = kThreads) {
     using T = typename Tr<DT>::T;
     __threadfence();
     __syncthreads();
@@ -100,7 +110,7 @@ __device__ __forceinline__ void arrive_and_finalize(const FinParams& f, uint32_t
             const uint32_t n0 = t * f.tile_units * 32u;
             const uint32_t n1 = min(f.N, n0 + f.tile_units * 32u);
             T* y = reinterpret_cast<T*>(f.y);
-            for (uint32_t n = n0 + threadIdx.x; n < n1; n += blockDim.x) {
+            for (uint32_t n = n0 + threadIdx.x; n < n1; n += nthreads) {
                 float v = __ldcg(&f.acc[n]);
                 __stcg(&f.acc[n], 0.0f);
                 y[n] = Tr<DT>::from_f(Tr<DT>::to_f(y[n]) + v);

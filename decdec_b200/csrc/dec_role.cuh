@@ -292,6 +292,7 @@ __device__ void dec_fetch(const DecParams& p, float* acc_g, uint32_t nrows, uint
 template <int DT>
 __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, unsigned char* sm) {
     using T = typename Tr<DT>::T;
+    if (threadIdx.x >= kThreads) return;   // launches shared with a wider GEMV role: extra warps leave
     const uint32_t rp = cta % p.n_rowparts;
     const uint32_t cp = cta / p.n_rowparts;
     // column part = a contiguous range of output tiles

@@ -122,7 +122,7 @@ __device__ void bcq_role(const BcqParams& p, const FinParams& f, uint32_t cta, u
             if (kw >= nwordrows) continue;
             const uint32_t g = (kw * 32) / p.group;
             const uint32_t* wrow = p.qweight + (size_t)kw * nbits * p.N;
-            const unsigned char* tbi = tb + it * 128;
+            const uint32_t tbi_s = (uint32_t)__cvta_generic_to_shared(tb) + it * 128;
             auto plane = [&](uint32_t pl, uint4 wa, uint4 wb) {
                 float al[8];
                 const size_t ai = ((size_t)g * nbits + pl) * p.N;
@@ -135,7 +135,7 @@ __device__ void bcq_role(const BcqParams& p, const FinParams& f, uint32_t cta, u
 #pragma unroll
                     for (int s = 0; s < 4; ++s) {
                         const uint32_t addr = __byte_perm(w[q], lb[s], sel[s]);
-                        a += *reinterpret_cast<const float*>(tbi + addr);
+                        a += lds_f32(tbi_s + addr);
                     }
                     y8[q] = fmaf(al[q], a, y8[q]);
                 }

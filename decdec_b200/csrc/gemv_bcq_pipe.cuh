@@ -1,0 +1,289 @@
+// Binary-coded (LUT-GEMM) GEMV role, TMA-pipelined variant for the common shapes.
+//
+// Same arithmetic and table trick as gemv_bcq.cuh (signed-subset-sum tables of the activations,
+// byte-permute addressing, bank-conflict-free lane layout), but the weight stream no longer passes
+// through registers: a producer thread moves a tile of [16 k-rows x bits planes] x 128 outputs (+ the
+// alpha and q_bias rows that go with them) per stage from HBM to shared memory with three tiled TMA
+// copies (cp.async.bulk.tensor.2d, completion counted on an mbarrier), several stages ahead of the
+// eight consumer warps.  HBM latency is then covered by bytes in flight (about 29 KB per stage, up to
+// 5 stages per SM) instead of by occupancy.  The tile lands densely (512-byte lines); the lanes of a
+// warp read it in a skewed order (k-row j reads the 16-byte groups (j + c) mod 8 and +4), so every
+// 128-bit shared load of a quarter warp touches eight different bank groups.
+//
+// Requirements (otherwise the register-staged kernel of gemv_bcq.cuh runs): N % 128 == 0,
+// K % 512 == 0, group size one of 32..512 dividing 512, at least two stages fit in shared memory.
+// Every wait on an mbarrier is bounded; on expiry the CTA raises the error word of the workspace
+// and leaves without touching the output.
+#pragma once
+#include "common.cuh"
+#include "gemv_bcq.cuh"
+#include <cuda.h>
+
+namespace dd {
+
+constexpr int kPipeStageN = 128;            // outputs per stage
+constexpr int kPipeLine = 512;              // bytes of one [k-row, plane] line of a stage (128 outputs)
+constexpr int kPipeThreads = 288;           // 8 consumer warps + 1 producer warp
+constexpr uint32_t kPipeWaitLimit = 1u << 22;
+
+struct PipeGeom {
+    uint32_t stages;         // pipeline depth S
+    uint32_t stage_bytes;    // bytes of one stage in shared memory
+    uint32_t w_bytes;        // weight part of a stage
+    uint32_t a_bytes;        // alpha part of a stage
+    uint32_t tile_stages;    // stages (128 outputs each) per CTA
+    uint32_t smem_bytes;     // dynamic shared memory of the launch
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false if the barrier did not flip within the limit or another thread gave up
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    for (uint32_t i = 0; i < kPipeWaitLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 63u && *abort_flag) return false;
+    }
+    *abort_flag = 1u;
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tma_2d_g2s(uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+struct PipeMaps {
+    CUtensorMap w;      // qweight as 2-D uint32 [K/32 * bits, N], box [16 * bits, 128]
+    CUtensorMap a;      // alpha   as 2-D       [K/group * bits, N], box [512/group * bits, 128]
+    CUtensorMap b;      // q_bias  as 2-D       [K/group, N], box [512/group, 128]
+};
+
+template <int DT>
+__device__ __forceinline__ void lds4f(const unsigned char* base, uint32_t elem, float* o) {
+    if constexpr (DT == FP32) {
+        const float4 v = *reinterpret_cast<const float4*>(base + elem * 4);
+        o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+    } else if constexpr (DT == FP16) {
+        const uint2 v = *reinterpret_cast<const uint2*>(base + elem * 2);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+        o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+    } else {
+        const uint2 v = *reinterpret_cast<const uint2*>(base + elem * 2);
+        o[0] = __uint_as_float(v.x << 16); o[1] = __uint_as_float(v.x & 0xffff0000u);
+        o[2] = __uint_as_float(v.y << 16); o[3] = __uint_as_float(v.y & 0xffff0000u);
+    }
+}
+
+// Shared memory: [tables 64 KB][rowsum 64 B][flags 16 B][full barriers 8x8 B][empty barriers 8x8 B][stages...]
+constexpr int kPipeHdr = (kBcqTableBytes + 64 + 16 + 64 + 64 + 127) & ~127;   // stages (TMA destinations) start 128-byte aligned
+static_assert(kPipeHdr % 128 == 0, "TMA destinations must be 128-byte aligned");
+
+template <int DT, int BITS>
+__device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const PipeGeom& geo, const PipeMaps& maps,
+                              uint32_t cta, unsigned char* sm) {
+    using T = typename Tr<DT>::T;
+    constexpr uint32_t ESZ = (DT == FP32) ? 4u : 2u;
+    float* tbl = reinterpret_cast<float*>(sm);
+    float* rowsum = reinterpret_cast<float*>(sm + kBcqTableBytes);
+    volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(sm + kBcqTableBytes + 64);
+    unsigned* s_flag = reinterpret_cast<unsigned*>(sm + kBcqTableBytes + 64 + 4);
+    const uint32_t bar_full = smem_u32(sm + kBcqTableBytes + 80);
+    const uint32_t bar_empty = bar_full + 64;
+    unsigned char* stage0 = sm + kPipeHdr;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t ks = cta % p.n_kslices;
+    const uint32_t tile = cta / p.n_kslices;
+    const uint32_t kbase = ks * kBcqSlice;
+    const uint32_t nst_total = p.N / kPipeStageN;
+    const uint32_t st0 = tile * geo.tile_stages;
+    const uint32_t nst = min(geo.tile_stages, nst_total - st0);
+    const uint32_t S = geo.stages;
+    const uint32_t groups = kBcqSlice / p.group;      // scale groups inside the K slice
+
+    if (tid == 0) {
+        *s_abort = 0u;
+        for (uint32_t s = 0; s < S; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 8);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 8) {
+        // ------------------------------ producer warp (one elected lane) -------------------------
+        const uint32_t tx = geo.w_bytes + geo.a_bytes + groups * kPipeStageN * ESZ;
+        uint32_t issued = 0;
+        if (lane == 0) {
+            for (uint32_t i = 0; i < nst; ++i) {
+                const uint32_t s = i % S, use = i / S;
+                if (use > 0 && !mbar_wait(bar_empty + 8 * s, (use - 1) & 1u, s_abort)) break;
+                const uint32_t full = bar_full + 8 * s;
+                mbar_expect_tx(full, tx);
+                const uint32_t n0 = (st0 + i) * kPipeStageN;
+                const uint32_t dst = smem_u32(stage0 + (size_t)s * geo.stage_bytes);
+                tma_2d_g2s(dst, &maps.w, n0, (kbase / 32) * BITS, full);
+                tma_2d_g2s(dst + geo.w_bytes, &maps.a, n0, (kbase / p.group) * BITS, full);
+                tma_2d_g2s(dst + geo.w_bytes + geo.a_bytes, &maps.b, n0, kbase / p.group, full);
+                issued = i + 1;
+            }
+            if (*s_abort) {
+                // drain: never leave the CTA with copies still landing in shared memory
+                const uint32_t first = issued > S ? issued - S : 0;
+                for (uint32_t i = first; i < issued; ++i) {
+                    volatile uint32_t never = 0;
+                    mbar_wait(bar_full + 8 * (i % S), (i / S) & 1u, &never);
+                }
+            }
+        }
+    } else {
+        // ------------------------------ consumer warps (8) ---------------------------------------
+        // build the 64 subset-sum tables of the slice: slot = (krow / 8) * 32 + (krow % 8) * 4 + byte
+        {
+            const uint32_t slot = (warp & 1) * 32 + lane;
+            const uint32_t qe = warp >> 1;
+            const uint32_t krow_b = (slot >> 5) * 8 + ((slot & 31) >> 2);
+            const uint32_t k0 = kbase + 32 * krow_b + 8 * (slot & 3);
+            const T* x = reinterpret_cast<const T*>(p.x);
+            float xv[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) xv[i] = Tr<DT>::to_f(x[k0 + i]);
+            float lo[8], hi[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                lo[e] = ((e & 1) ? xv[0] : -xv[0]) + ((e & 2) ? xv[1] : -xv[1]) + ((e & 4) ? xv[2] : -xv[2]);
+                hi[e] = ((e & 1) ? xv[3] : -xv[3]) + ((e & 2) ? xv[4] : -xv[4]) + ((e & 4) ? xv[5] : -xv[5]);
+            }
+            const float top = ((qe & 1) ? xv[6] : -xv[6]) + ((qe & 2) ? xv[7] : -xv[7]);
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+                const float th = top + hi[h];
+#pragma unroll
+                for (int l = 0; l < 8; ++l) tbl[(qe * 64 + h * 8 + l) * 64 + slot] = th + lo[l];
+            }
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (tid < 16) {
+            const uint32_t base = (tid >> 3) * 32 + (tid & 7) * 4;
+            rowsum[tid] = tbl[255 * 64 + base] + tbl[255 * 64 + base + 1] + tbl[255 * 64 + base + 2] + tbl[255 * 64 + base + 3];
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+
+        // warp = (k half, 32-output block); lane = (k-row j, c).  Row j reads the 16-byte groups
+        // tA = (j + c) & 7 and tB = tA ^ 4 of the block's 128-byte line segment.
+        const uint32_t j = lane & 7, c = lane >> 3;
+        const uint32_t blk = warp & 3, khalf = warp >> 2;
+        const uint32_t krow = khalf * 8 + j;
+        const uint32_t tA = (j + c) & 7, tB = tA ^ 4;
+        uint32_t sel[4], lb[4];
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            const uint32_t byte = (s + c) & 3;
+            sel[s] = 0x6504u | (byte << 4);
+            lb[s] = (4 * j + byte) * 4;
+        }
+        const uint32_t tbi_s = smem_u32(tbl) + khalf * 128;
+        const float sx = rowsum[krow];
+        const uint32_t g = (32 * krow) / p.group;          // scale group of this lane's k-row inside the slice
+        const uint32_t nA = blk * 32 + 4 * tA, nB = blk * 32 + 4 * tB;
+        // partner lanes of the reduction over k-rows (lanes sharing (j + c) & 3 hold the same two groups)
+        const uint32_t p4 = lane ^ 4, p2 = lane ^ 18;
+        const uint32_t p1 = (j ^ 1) + 8 * (((j & 1) ? c + 1 : c + 3) & 3);
+        const bool swapAB = (tA & 4) != 0;                  // after the swap X = group r, Y = group r + 4, r = tA & 3
+        const uint32_t r = tA & 3;
+        const uint32_t n_out = blk * 32 + ((j & 4) ? 16 : 0) + 4 * r + (j & 3);
+
+        for (uint32_t i = 0; i < nst; ++i) {
+            const uint32_t s = i % S;
+            if (!mbar_wait(bar_full + 8 * s, (i / S) & 1u, s_abort)) break;
+            const unsigned char* st = stage0 + (size_t)s * geo.stage_bytes;
+            const unsigned char* wl = st + krow * (BITS * kPipeLine);
+            const unsigned char* al = st + geo.w_bytes + (g * BITS) * (kPipeStageN * ESZ);
+            const unsigned char* bl = st + geo.w_bytes + geo.a_bytes + g * (kPipeStageN * ESZ);
+            uint4 wA[BITS], wB[BITS];
+            float a8[BITS][8], y8[8];
+#pragma unroll
+            for (int pl = 0; pl < BITS; ++pl) {
+                wA[pl] = *reinterpret_cast<const uint4*>(wl + pl * kPipeLine + nA * 4);
+                wB[pl] = *reinterpret_cast<const uint4*>(wl + pl * kPipeLine + nB * 4);
+                lds4f<DT>(al + pl * (kPipeStageN * ESZ), nA, a8[pl]);
+                lds4f<DT>(al + pl * (kPipeStageN * ESZ), nB, a8[pl] + 4);
+            }
+            lds4f<DT>(bl, nA, y8);
+            lds4f<DT>(bl, nB, y8 + 4);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);      // stage data is in registers: release it
+#pragma unroll
+            for (int q = 0; q < 8; ++q) y8[q] *= sx;
+#pragma unroll
+            for (int pl = 0; pl < BITS; ++pl) {
+                const uint32_t wq[8] = {wA[pl].x, wA[pl].y, wA[pl].z, wA[pl].w, wB[pl].x, wB[pl].y, wB[pl].z, wB[pl].w};
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    float v[16];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int ss = 0; ss < 4; ++ss) v[q * 4 + ss] = lds_f32(tbi_s + __byte_perm(wq[hh * 4 + q], lb[ss], sel[ss]));
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        y8[hh * 4 + q] = fmaf(a8[pl][hh * 4 + q], (v[q * 4] + v[q * 4 + 1]) + (v[q * 4 + 2] + v[q * 4 + 3]), y8[hh * 4 + q]);
+                }
+            }
+            // X = values of group r, Y = values of group r + 4; reduce over the 8 k-row lanes, halving
+            float y4[4], y2[2], y1;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float X = swapAB ? y8[q + 4] : y8[q];
+                const float Y = swapAB ? y8[q] : y8[q + 4];
+                const float send = (j & 4) ? X : Y;
+                const float keep = (j & 4) ? Y : X;
+                y4[q] = keep + __shfl_sync(0xffffffffu, send, p4);
+            }
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const float send = (j & 2) ? y4[q] : y4[q + 2];
+                const float keep = (j & 2) ? y4[q + 2] : y4[q];
+                y2[q] = keep + __shfl_sync(0xffffffffu, send, p2);
+            }
+            {
+                const float send = (j & 1) ? y2[0] : y2[1];
+                const float keep = (j & 1) ? y2[1] : y2[0];
+                y1 = keep + __shfl_sync(0xffffffffu, send, p1);
+            }
+            atomicAdd(&f.acc[(st0 + i) * kPipeStageN + n_out], y1);
+        }
+    }
+    __syncthreads();
+    if (*s_abort) {
+        if (tid == 0) atomicExch(f.err, 1u);
+        return;
+    }
+    arrive_and_finalize<DT>(f, tile, tile + 1, s_flag, kPipeThreads);
+}
+
+}  // namespace dd

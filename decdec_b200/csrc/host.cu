@@ -38,6 +38,7 @@ constexpr uint32_t kTicketCap = 1u << 13;
 struct Workspace {
     float* acc = nullptr;
     unsigned* tickets = nullptr;
+    unsigned* err = nullptr;     // last word of the ticket allocation
 };
 
 std::mutex g_mu;
@@ -65,9 +66,10 @@ int get_workspace(cudaStream_t stream, Workspace* out) {
     }
     Workspace w;
     if (cudaMalloc(&w.acc, kAccCap * sizeof(float)) != cudaSuccess) return fail(DECDEC_E_NOMEM, "cudaMalloc(accumulator) failed");
-    if (cudaMalloc(&w.tickets, kTicketCap * sizeof(unsigned)) != cudaSuccess) { cudaFree(w.acc); return fail(DECDEC_E_NOMEM, "cudaMalloc(tickets) failed"); }
+    if (cudaMalloc(&w.tickets, (kTicketCap + 4) * sizeof(unsigned)) != cudaSuccess) { cudaFree(w.acc); return fail(DECDEC_E_NOMEM, "cudaMalloc(tickets) failed"); }
     DD_CUDA(cudaMemset(w.acc, 0, kAccCap * sizeof(float)));
-    DD_CUDA(cudaMemset(w.tickets, 0, kTicketCap * sizeof(unsigned)));
+    DD_CUDA(cudaMemset(w.tickets, 0, (kTicketCap + 4) * sizeof(unsigned)));
+    w.err = w.tickets + kTicketCap;
     DD_CUDA(cudaDeviceSynchronize());
     g_ws[{dev, stream}] = w;
     if (!g_ws_first.count(dev)) g_ws_first[dev] = w;
@@ -173,6 +175,7 @@ int setup_fin(FinParams* f, const Workspace& ws, void* y, uint32_t N, uint32_t t
     if (N > kAccCap) return fail(DECDEC_E_UNSUPPORTED, "out_features %u exceeds the accumulator capacity %u", N, kAccCap);
     f->acc = ws.acc;
     f->tickets = ws.tickets;
+    f->err = ws.err;
     f->y = y;
     f->N = N;
     f->tile_units = tile_units;
@@ -240,8 +243,15 @@ int run_bcq(Config* c, const void* x, void* y, const int32_t* qw, const void* al
     uint32_t tile_units = cdiv(units, tiles_target);
     tile_units = cdiv(tile_units, 8) * 8;
     tile_units = env_u32("DECDEC_BCQ_TILE_UNITS", tile_units);
+    PipeGeom geo;
+    const bool pipe = env_u32("DECDEC_BCQ_PIPE", 1) && bcq_pipe_geometry(N, K, g.bits, g.group, dtype, g.n_kslices, &geo);
     FinParams f;
-    if (int r = setup_fin(&f, ws, y, N, tile_units, g.n_kslices)) return r;
+    if (pipe) {
+        tile_units = geo.tile_stages * (kPipeStageN / 32);
+        if (int r = setup_fin(&f, ws, y, N, tile_units, g.n_kslices)) return r;
+    } else {
+        if (int r = setup_fin(&f, ws, y, N, tile_units, g.n_kslices)) return r;
+    }
     g.n_cta = g.n_kslices * f.n_tiles;
     DecParams d;
     memset(&d, 0, sizeof(d));
@@ -249,7 +259,8 @@ int run_bcq(Config* c, const void* x, void* y, const int32_t* qw, const void* al
         if (int r = fill_dec(c, x, true, f.n_tiles, &d)) return r;
         if (d.n_cta) f.expected += d.n_rowparts;
     }
-    DD_CUDA(launch_bcq(dtype, g, d, f, s));
+    if (pipe) DD_CUDA(launch_bcq_pipe(dtype, g, d, f, geo, s));
+    else DD_CUDA(launch_bcq(dtype, g, d, f, s));
     return 0;
 }
 

@@ -1,6 +1,7 @@
 // Binary-coded GEMV launches (entry points `lutgemm_gemv`, `dec_lutgemm`).
 #include "internal.h"
 #include "dec_role.cuh"
+#include "gemv_bcq_pipe.cuh"
 
 namespace dd {
 
@@ -25,6 +26,105 @@ static cudaError_t go(const BcqParams& g, const DecParams& d, const FinParams& f
     }
     k_bcq<DT, BITS><<<d.n_cta + g.n_cta, kThreads, smem, s>>>(g, d, f);
     return cudaGetLastError();
+}
+
+template <int DT, int BITS>
+__global__ void __launch_bounds__(kPipeThreads, 1)
+k_bcq_pipe(const __grid_constant__ BcqParams g, const __grid_constant__ DecParams d, const __grid_constant__ FinParams f,
+           const __grid_constant__ PipeGeom geo, const __grid_constant__ PipeMaps maps) {
+    extern __shared__ __align__(128) unsigned char sm[];
+    if (blockIdx.x < d.n_cta) dec_role<DT>(d, f, blockIdx.x, sm);
+    else bcq_pipe_role<DT, BITS>(g, f, geo, maps, blockIdx.x - d.n_cta, sm);
+}
+
+template <int DT, int BITS>
+static cudaError_t go_pipe(const BcqParams& g, const DecParams& d, const FinParams& f, const PipeGeom& geo, const PipeMaps& maps,
+                           cudaStream_t s) {
+    static size_t configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && configured[dev] < geo.smem_bytes) {
+        cudaError_t e = cudaFuncSetAttribute(k_bcq_pipe<DT, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        configured[dev] = 227 * 1024;
+    }
+    k_bcq_pipe<DT, BITS><<<d.n_cta + g.n_cta, kPipeThreads, geo.smem_bytes, s>>>(g, d, f, geo, maps);
+    return cudaGetLastError();
+}
+
+template <int DT>
+static cudaError_t pipe_by_bits(const BcqParams& g, const DecParams& d, const FinParams& f, const PipeGeom& geo,
+                                const PipeMaps& maps, cudaStream_t s) {
+    switch (g.bits) {
+        case 2: return go_pipe<DT, 2>(g, d, f, geo, maps, s);
+        case 3: return go_pipe<DT, 3>(g, d, f, geo, maps, s);
+        default: return go_pipe<DT, 4>(g, d, f, geo, maps, s);
+    }
+}
+
+// cuTensorMapEncodeTiled is fetched from the driver at run time (no link-time dependency on libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+static bool encode_2d(CUtensorMap* m, const void* base, int dt_bytes, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * (uint64_t)dt_bytes};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType t = dt_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+    return fn(m, t, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+cudaError_t launch_bcq_pipe(int dt, const BcqParams& g, const DecParams& d, const FinParams& f, const PipeGeom& geo, cudaStream_t s) {
+    PipeMaps maps;
+    const int esz = dt == FP32 ? 4 : 2;
+    const uint32_t groups = kBcqSlice / g.group;
+    if (!encode_2d(&maps.w, g.qweight, 4, (uint64_t)(g.K / 32) * g.bits, g.N, 16 * g.bits, kPipeStageN) ||
+        !encode_2d(&maps.a, g.alpha, esz, (uint64_t)(g.K / g.group) * g.bits, g.N, groups * g.bits, kPipeStageN) ||
+        !encode_2d(&maps.b, g.q_bias, esz, (uint64_t)(g.K / g.group), g.N, groups, kPipeStageN))
+        return cudaErrorInvalidValue;
+    switch (dt) {
+        case FP32: return pipe_by_bits<FP32>(g, d, f, geo, maps, s);
+        case FP16: return pipe_by_bits<FP16>(g, d, f, geo, maps, s);
+        default: return pipe_by_bits<BF16>(g, d, f, geo, maps, s);
+    }
+}
+
+// Stage geometry of the pipelined kernel; returns false if the shape is not eligible.
+bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, int dt, uint32_t n_kslices, PipeGeom* geo) {
+    if (N % kPipeStageN || K % kBcqSlice || bits < 2 || bits > 4) return false;
+    if (group < 32 || group > (uint32_t)kBcqSlice || kBcqSlice % group) return false;
+    const uint32_t esz = dt == FP32 ? 4 : 2;
+    const uint32_t groups = kBcqSlice / group;
+    geo->w_bytes = 16 * bits * kPipeLine;
+    geo->a_bytes = groups * bits * kPipeStageN * esz;
+    geo->stage_bytes = (geo->w_bytes + geo->a_bytes + groups * kPipeStageN * esz + 127u) & ~127u;
+    const uint32_t budget = 227 * 1024 - kPipeHdr;
+    uint32_t smax = budget / geo->stage_bytes;
+    if (smax > 6) smax = 6;
+    if (smax < 2) return false;
+    const uint32_t nst_total = N / kPipeStageN;
+    // one CTA (16 consumer warps) per SM; tiles sized so that the grid is at most one wave
+    uint32_t per1 = 148 / n_kslices; if (per1 == 0) per1 = 1;
+    geo->tile_stages = (nst_total + per1 - 1) / per1;
+    geo->stages = geo->tile_stages < smax ? geo->tile_stages : smax;
+    geo->smem_bytes = kPipeHdr + geo->stages * geo->stage_bytes;
+    if (geo->smem_bytes < (uint32_t)DecSmem::kBytes) geo->smem_bytes = DecSmem::kBytes;
+    return true;
 }
 
 template <int DT>

@@ -23,7 +23,7 @@ namespace dd {
 
 constexpr int kPipeStageN = 128;            // outputs per stage
 constexpr int kPipeLine = 512;              // bytes of one [k-row, plane] line of a stage (128 outputs)
-constexpr int kPipeThreads = 288;           // 8 consumer warps + 1 producer warp
+constexpr int kPipeThreads = 544;           // 2 groups of 8 consumer warps + 1 producer warp
 constexpr uint32_t kPipeWaitLimit = 1u << 22;
 
 struct PipeGeom {
@@ -134,7 +134,7 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
     }
     __syncthreads();
 
-    if (warp == 8) {
+    if (warp == 16) {
         // ------------------------------ producer warp (one elected lane) -------------------------
         const uint32_t tx = geo.w_bytes + geo.a_bytes + groups * kPipeStageN * ESZ;
         uint32_t issued = 0;
@@ -162,7 +162,8 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
         }
     } else {
         // ------------------------------ consumer warps (8) ---------------------------------------
-        // build the 64 subset-sum tables of the slice: slot = (krow / 8) * 32 + (krow % 8) * 4 + byte
+        // build the 64 subset-sum tables of the slice: slot = (krow / 8) * 32 + (krow % 8) * 4 + byte;
+        // a thread fills the 32 entries whose bits 5..7 equal warp / 2
         {
             const uint32_t slot = (warp & 1) * 32 + lane;
             const uint32_t qe = warp >> 1;
@@ -172,31 +173,33 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
             float xv[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) xv[i] = Tr<DT>::to_f(x[k0 + i]);
-            float lo[8], hi[8];
+            float lo[8], hi[4];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
+            for (int e = 0; e < 8; ++e)
                 lo[e] = ((e & 1) ? xv[0] : -xv[0]) + ((e & 2) ? xv[1] : -xv[1]) + ((e & 4) ? xv[2] : -xv[2]);
-                hi[e] = ((e & 1) ? xv[3] : -xv[3]) + ((e & 2) ? xv[4] : -xv[4]) + ((e & 4) ? xv[5] : -xv[5]);
-            }
-            const float top = ((qe & 1) ? xv[6] : -xv[6]) + ((qe & 2) ? xv[7] : -xv[7]);
 #pragma unroll
-            for (int h = 0; h < 8; ++h) {
+            for (int e = 0; e < 4; ++e) hi[e] = ((e & 1) ? xv[3] : -xv[3]) + ((e & 2) ? xv[4] : -xv[4]);
+            const float top = ((qe & 1) ? xv[5] : -xv[5]) + ((qe & 2) ? xv[6] : -xv[6]) + ((qe & 4) ? xv[7] : -xv[7]);
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
                 const float th = top + hi[h];
 #pragma unroll
-                for (int l = 0; l < 8; ++l) tbl[(qe * 64 + h * 8 + l) * 64 + slot] = th + lo[l];
+                for (int l = 0; l < 8; ++l) tbl[(qe * 32 + h * 8 + l) * 64 + slot] = th + lo[l];
             }
         }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, 512;" ::: "memory");
         if (tid < 16) {
             const uint32_t base = (tid >> 3) * 32 + (tid & 7) * 4;
             rowsum[tid] = tbl[255 * 64 + base] + tbl[255 * 64 + base + 1] + tbl[255 * 64 + base + 2] + tbl[255 * 64 + base + 3];
         }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, 512;" ::: "memory");
 
+        // two groups of 8 warps take alternate stages.  Inside a group:
         // warp = (k half, 32-output block); lane = (k-row j, c).  Row j reads the 16-byte groups
         // tA = (j + c) & 7 and tB = tA ^ 4 of the block's 128-byte line segment.
         const uint32_t j = lane & 7, c = lane >> 3;
-        const uint32_t blk = warp & 3, khalf = warp >> 2;
+        const uint32_t grp = warp >> 3;
+        const uint32_t blk = warp & 3, khalf = (warp >> 2) & 1;
         const uint32_t krow = khalf * 8 + j;
         const uint32_t tA = (j + c) & 7, tB = tA ^ 4;
         uint32_t sel[4], lb[4];
@@ -217,43 +220,37 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
         const uint32_t r = tA & 3;
         const uint32_t n_out = blk * 32 + ((j & 4) ? 16 : 0) + 4 * r + (j & 3);
 
-        for (uint32_t i = 0; i < nst; ++i) {
+        for (uint32_t i = grp; i < nst; i += 2) {
             const uint32_t s = i % S;
             if (!mbar_wait(bar_full + 8 * s, (i / S) & 1u, s_abort)) break;
             const unsigned char* st = stage0 + (size_t)s * geo.stage_bytes;
             const unsigned char* wl = st + krow * (BITS * kPipeLine);
             const unsigned char* al = st + geo.w_bytes + (g * BITS) * (kPipeStageN * ESZ);
             const unsigned char* bl = st + geo.w_bytes + geo.a_bytes + g * (kPipeStageN * ESZ);
-            uint4 wA[BITS], wB[BITS];
-            float a8[BITS][8], y8[8];
-#pragma unroll
-            for (int pl = 0; pl < BITS; ++pl) {
-                wA[pl] = *reinterpret_cast<const uint4*>(wl + pl * kPipeLine + nA * 4);
-                wB[pl] = *reinterpret_cast<const uint4*>(wl + pl * kPipeLine + nB * 4);
-                lds4f<DT>(al + pl * (kPipeStageN * ESZ), nA, a8[pl]);
-                lds4f<DT>(al + pl * (kPipeStageN * ESZ), nB, a8[pl] + 4);
-            }
+            float y8[8];
             lds4f<DT>(bl, nA, y8);
             lds4f<DT>(bl, nB, y8 + 4);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + 8 * s);      // stage data is in registers: release it
 #pragma unroll
             for (int q = 0; q < 8; ++q) y8[q] *= sx;
-#pragma unroll
+#pragma unroll 1
             for (int pl = 0; pl < BITS; ++pl) {
-                const uint32_t wq[8] = {wA[pl].x, wA[pl].y, wA[pl].z, wA[pl].w, wB[pl].x, wB[pl].y, wB[pl].z, wB[pl].w};
+                const uint4 wA = *reinterpret_cast<const uint4*>(wl + pl * kPipeLine + nA * 4);
+                const uint4 wB = *reinterpret_cast<const uint4*>(wl + pl * kPipeLine + nB * 4);
+                float a8[8];
+                lds4f<DT>(al + pl * (kPipeStageN * ESZ), nA, a8);
+                lds4f<DT>(al + pl * (kPipeStageN * ESZ), nB, a8 + 4);
+                const uint32_t wq[8] = {wA.x, wA.y, wA.z, wA.w, wB.x, wB.y, wB.z, wB.w};
+                float v[32];
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    float v[16];
+                for (int q = 0; q < 8; ++q)
 #pragma unroll
-                    for (int q = 0; q < 4; ++q)
+                    for (int ss = 0; ss < 4; ++ss) v[q * 4 + ss] = lds_f32(tbi_s + __byte_perm(wq[q], lb[ss], sel[ss]));
 #pragma unroll
-                        for (int ss = 0; ss < 4; ++ss) v[q * 4 + ss] = lds_f32(tbi_s + __byte_perm(wq[hh * 4 + q], lb[ss], sel[ss]));
-#pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        y8[hh * 4 + q] = fmaf(a8[pl][hh * 4 + q], (v[q * 4] + v[q * 4 + 1]) + (v[q * 4 + 2] + v[q * 4 + 3]), y8[hh * 4 + q]);
-                }
+                for (int q = 0; q < 8; ++q)
+                    y8[q] = fmaf(a8[q], (v[q * 4] + v[q * 4 + 1]) + (v[q * 4 + 2] + v[q * 4 + 3]), y8[q]);
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);      // all shared reads of the stage are done
             // X = values of group r, Y = values of group r + 4; reduce over the 8 k-row lanes, halving
             float y4[4], y2[2], y1;
 #pragma unroll

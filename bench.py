@@ -42,13 +42,23 @@ BITS, GROUP = 3, 128
 def projections(model: str, tp: int = 1, rank: int = 0):
     """[(name, N_local, K_local, parallel)] of one layer; fused wqkv / w1w3 as in the reference model
     (end-to-end/model.py:266,331)."""
+    from decdec_b200 import tp as tpl
     _, d, hq, hkv, hd, ffn = MODELS[model]
     qkv = (hq + 2 * hkv) * hd
+
+    def col(n):
+        a, b = tpl.split_even(n, tp, 128 if n % (128 * tp) == 0 else 32)[rank]
+        return b - a
+
+    def row(k):
+        a, b = tpl.k_ranges(k, tp, GROUP)[rank]
+        return b - a
+
     return [
-        ("wqkv", qkv // tp, d, "col"),
-        ("wo", d, d // tp, "row"),
-        ("w1w3", 2 * ffn // tp, d, "col"),
-        ("w2", d, ffn // tp, "row"),
+        ("wqkv", col(qkv), d, "col"),
+        ("wo", d, row(d), "row"),
+        ("w1w3", col(2 * ffn), d, "col"),
+        ("w2", d, row(ffn), "row"),
     ]
 
 

@@ -75,4 +75,4 @@ def test_bench_accounting():
     p = bench.projections("llama3-8b")
     assert [(n, k) for _, n, k, _ in p] == [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]
     p8 = bench.projections("llama3-70b", tp=8)
-    assert [(n, k) for _, n, k, _ in p8] == [(1280, 8192), (8192, 1024), (7168, 8192), (8192, 3584)]
+    assert [(n, k) for _, n, k, _ in p8] == [(1280, 8192), (8192, 1024), (7168, 8192), (8192, 4096)]   # 28 chunks -> 4,4,4,4,3,3,3,3

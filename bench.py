@@ -394,9 +394,15 @@ def main():
         }
         if cpu:
             line["cpu_baseline"] = cpu
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if dist is not None:
-        dist.destroy_process_group()
+        # graphs that captured NCCL work must go before the communicator; leave without running
+        # interpreter-exit destructors, which can block on a communicator with captured collectives
+        graphs.clear()
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

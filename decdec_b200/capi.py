@@ -57,6 +57,7 @@ SIGNATURES = {
     "decdec_anyprec_gemv": (_i, [_vp, _vp, _vp, _u32, _vp, _u32, _u32, _i, _i, _vp]),
     "decdec_lutgemm_gemv": (_i, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _i, _i, _i, _vp]),
     "decdec_sqllm_gemv": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _i, _i, _vp]),
+    "decdec_lutgemm_gemv_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _i, _i, _i, _vp]),
     "decdec_anyprec_dequant": (_i, [_vp, _vp, _vp, _u32, _u32, _i, _i, _vp]),
     "decdec_dec_anyprec": (_i, [_up, _vp, _vp, _vp, _u32, _vp, _u32, _u32, _i, _i, _vp]),
     "decdec_dec_lutgemm": (_i, [_up, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _i, _i, _i, _vp]),

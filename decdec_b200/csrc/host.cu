@@ -363,6 +363,11 @@ int run_dummy(int dummy_sm, long long iters, void* stream, F gemv) {
 
 }  // namespace
 
+namespace dd {
+// lets other translation units of the library record the message returned by decdec_last_error()
+int set_last_error(int code, const char* msg) { return fail(code, "%s", msg); }
+}  // namespace dd
+
 extern "C" {
 
 const char* decdec_last_error(void) { return g_err; }

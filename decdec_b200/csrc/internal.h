@@ -19,6 +19,7 @@ cudaError_t launch_ap_dequant(int dt, const uint32_t* qweight, const void* lut, 
                               uint32_t bits, cudaStream_t s);
 cudaError_t launch_burner(int blocks, long long iters, cudaStream_t s);
 
+int set_last_error(int code, const char* msg);
 size_t dec_only_smem();
 size_t anyprec_smem(uint32_t K, bool fast3);
 size_t sqllm_smem(uint32_t K);

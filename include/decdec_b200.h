@@ -100,6 +100,19 @@ int decdec_lutgemm_gemv(const void* x_dev, void* y_dev, const int32_t* qweight, 
 int decdec_sqllm_gemv(const void* x_dev, void* y_dev, const int32_t* qweight, const void* lut,
                       uint32_t N, uint32_t K, int bitwidth, int dtype, void* stream);
 
+/* lutgemm GEMV that allocates nothing.  NO COUNTERPART IN THE REFERENCE.
+ * Same arguments and result as decdec_lutgemm_gemv.  The accumulator workspace that the other entry
+ * points obtain with cudaMalloc is replaced by a fixed array inside the library (held by every GPU
+ * that loads the library until the process exits), so the call is usable by hosts that may not call
+ * cudaMalloc at that point: plug-ins of an application that owns all device memory, real-time loops,
+ * code that is already inside a stream capture.  Limits and duties of the caller:
+ *   - out_features <= 32768, otherwise DECDEC_E_UNSUPPORTED;
+ *   - the first call on a device resolves the array's address; make it before any stream capture;
+ *   - all calls on one GPU share the array: calls that overlap in time on the GPU race. */
+int decdec_lutgemm_gemv_noalloc(const void* x_dev, void* y_dev, const int32_t* qweight, const void* alpha,
+                                const void* q_bias, uint32_t N, uint32_t K, int bitwidth, int group_size, int dtype,
+                                void* stream);
+
 /* anyprec_dequant (reference: decdec.cu:386-393): out_dev dtype [N, K] dense weights. */
 int decdec_anyprec_dequant(const int32_t* qweight, const void* lut, void* out_dev,
                            uint32_t N, uint32_t K, int bitwidth, int dtype, void* stream);

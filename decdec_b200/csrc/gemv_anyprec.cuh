@@ -6,7 +6,7 @@
 // words); bit 31-8j-r of word t of a block holds channel block_start + 8*E*j + 8*t + r; plane 0 is
 // the most significant code bit.
 //
-// 3-bit fast path: one warp per output row, 16-byte loads of four plane words per lane; the 8-entry
+// 3-bit fast path: one warp per output row, coalesced loads of four plane words per lane; the 8-entry
 // fp16 LUT of the row lives in four registers split into a low-byte and a high-byte table, codes are
 // turned into byte-permute selectors (three logic ops per 8 codes) and each permute looks up four
 // table bytes at once - no shared-memory LUT, hence no bank conflicts.  Activations are staged in
@@ -92,15 +92,22 @@ __device__ void ap3_role(const ApParams& p, const FinParams& f, uint32_t cta, un
         const uint32_t* row = p.qweight + (size_t)n * nwords;
         float facc = 0.0f;
         for (uint32_t wb = 0; wb < nwords; wb += 128) {
-            const uint32_t wi0 = wb + 4 * lane;
+            // lane handles words wb + 32*u + lane: coalesced 128-byte loads per plane, and consecutive
+            // lanes read consecutive 16-byte activation groups (no shared-memory bank conflicts)
+            const uint32_t wi0 = wb + lane;
             if (wi0 >= nwords) continue;
-            const uint4 A = ldg_stream(reinterpret_cast<const uint4*>(row + wi0));
-            const uint4 B = ldg_stream(reinterpret_cast<const uint4*>(row + plane_stride + wi0));
-            const uint4 C = ldg_stream(reinterpret_cast<const uint4*>(row + 2 * plane_stride + wi0));
-            const uint32_t aw[4] = {A.x, A.y, A.z, A.w}, bw[4] = {B.x, B.y, B.z, B.w}, cw[4] = {C.x, C.y, C.z, C.w};
+            uint32_t aw[4], bw[4], cw[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const uint32_t wi = wi0 + u;
+                const bool ok = wi0 + 32 * u < nwords;
+                aw[u] = ok ? ldg_stream(row + wi0 + 32 * u) : 0u;
+                bw[u] = ok ? ldg_stream(row + plane_stride + wi0 + 32 * u) : 0u;
+                cw[u] = ok ? ldg_stream(row + 2 * plane_stride + wi0 + 32 * u) : 0u;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t wi = wi0 + 32 * u;
+                if (wi >= nwords) break;
                 const uint32_t blk = wi >> 5, t = wi & 31u;
                 const uint32_t E = (blk == nfull) ? tailE : 32u;
                 const T* xb = sx + blk * 1024u + 8u * t;

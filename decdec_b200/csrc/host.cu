@@ -284,6 +284,9 @@ int run_anyprec(Config* c, const void* x, void* y, const int32_t* qw, uint32_t p
     const uint32_t target = env_u32("DECDEC_AP_CTAS", 592);
     uint32_t tile_units = cdiv(units, target);
     tile_units = env_u32("DECDEC_AP_TILE_UNITS", tile_units);
+    ApPipeGeom pgeo;
+    const bool pipe = env_u32("DECDEC_AP_PIPE", 1) && anyprec_pipe_geometry(N, K, g.bits, &pgeo);
+    if (pipe) tile_units = pgeo.rows_per_cta / 32;
     FinParams f;
     if (int r = setup_fin(&f, ws, y, N, tile_units, 1)) return r;
     g.n_cta = f.n_tiles;
@@ -294,6 +297,11 @@ int run_anyprec(Config* c, const void* x, void* y, const int32_t* qw, uint32_t p
         if (d.n_cta) f.expected += d.n_rowparts;
     }
     g.direct = d.n_cta ? 0u : 1u;
+    if (pipe) {
+        g.direct = 0u;
+        DD_CUDA(launch_anyprec_pipe(dtype, g, d, f, pgeo, s));
+        return 0;
+    }
     const bool fast3 = bits == 3 && (K % 128u) == 0u;
     if (anyprec_smem(K, fast3) > 200 * 1024) return fail(DECDEC_E_UNSUPPORTED, "anyprec: in_features %u too large for shared-memory staging", K);
     DD_CUDA(launch_anyprec(dtype, g, d, f, s));

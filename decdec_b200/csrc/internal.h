@@ -5,6 +5,7 @@
 #include "gemv_anyprec.cuh"
 #include "gemv_sqllm.cuh"
 #include "gemv_bcq_pipe.cuh"
+#include "gemv_anyprec_pipe.cuh"
 
 namespace dd {
 
@@ -14,6 +15,8 @@ cudaError_t launch_bcq(int dt, const BcqParams& g, const DecParams& d, const Fin
 bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, int dt, uint32_t n_kslices, PipeGeom* geo);
 cudaError_t launch_bcq_pipe(int dt, const BcqParams& g, const DecParams& d, const FinParams& f, const PipeGeom& geo, cudaStream_t s);
 cudaError_t launch_anyprec(int dt, const ApParams& g, const DecParams& d, const FinParams& f, cudaStream_t s);
+bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* geo);
+cudaError_t launch_anyprec_pipe(int dt, const ApParams& g, const DecParams& d, const FinParams& f, const ApPipeGeom& geo, cudaStream_t s);
 cudaError_t launch_sqllm(int dt, const SqParams& g, const DecParams& d, const FinParams& f, cudaStream_t s);
 cudaError_t launch_ap_dequant(int dt, const uint32_t* qweight, const void* lut, void* out, uint32_t N, uint32_t K,
                               uint32_t bits, cudaStream_t s);

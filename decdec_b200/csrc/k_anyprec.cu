@@ -1,6 +1,7 @@
 // Any-precision launches (entry points `anyprec_gemv`, `dec_anyprec`, `anyprec_dequant`).
 #include "internal.h"
 #include "dec_role.cuh"
+#include "gemv_anyprec_pipe.cuh"
 
 namespace dd {
 
@@ -38,6 +39,57 @@ cudaError_t launch_anyprec(int dt, const ApParams& g, const DecParams& d, const 
     const bool fast3 = g.bits == 3 && (g.K % 128u) == 0u;
     if (dt == FP16) return fast3 ? go<FP16, true>(g, d, f, s) : go<FP16, false>(g, d, f, s);
     return fast3 ? go<BF16, true>(g, d, f, s) : go<BF16, false>(g, d, f, s);
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kApPipeThreads, 1)
+k_anyprec_pipe(const __grid_constant__ ApParams g, const __grid_constant__ DecParams d, const __grid_constant__ FinParams f,
+               const __grid_constant__ ApPipeGeom geo) {
+    extern __shared__ __align__(128) unsigned char sm[];
+    if (blockIdx.x < d.n_cta) dec_role<DT>(d, f, blockIdx.x, sm);
+    else ap3_pipe_role<DT>(g, f, geo, blockIdx.x - d.n_cta, sm);
+}
+
+// Stage geometry of the pipelined 3-bit kernel; false if the shape is not eligible.
+bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* geo) {
+    if (bits != 3 || K % 128u || K > 32768u || N == 0) return false;
+    const uint32_t rowbytes = K / 8;
+    geo->segs = (K + 4095) / 4096;
+    uint32_t R = 16 / geo->segs;
+    if (R == 0) return false;
+    while (R & (R - 1)) R &= R - 1;                      // largest power of two <= 16 / segs
+    geo->rows_per_stage = R;
+    geo->x_bytes = (K * 2 + 127u) & ~127u;
+    geo->stage_bytes = (R * (3 * rowbytes + 16) + 127u) & ~127u;
+    const uint32_t budget = 227 * 1024 - kApPipeHdr - geo->x_bytes;
+    uint32_t smax = budget / geo->stage_bytes;
+    if (smax > 8) smax = 8;
+    if (smax < 2) return false;
+    uint32_t rows = (N + 147) / 148;
+    rows = ((rows + 31) / 32) * 32;
+    geo->rows_per_cta = rows;
+    const uint32_t nst = rows / R;
+    geo->stages = nst < smax ? nst : smax;
+    geo->smem_bytes = kApPipeHdr + geo->x_bytes + geo->stages * geo->stage_bytes;
+    if (geo->smem_bytes < (uint32_t)DecSmem::kBytes) geo->smem_bytes = DecSmem::kBytes;
+    return true;
+}
+
+cudaError_t launch_anyprec_pipe(int dt, const ApParams& g, const DecParams& d, const FinParams& f, const ApPipeGeom& geo, cudaStream_t s) {
+    static bool configured[64][2] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int di = dt == FP16 ? 0 : 1;
+    if (dev < 64 && !configured[dev][di]) {
+        cudaError_t e = dt == FP16
+            ? cudaFuncSetAttribute(k_anyprec_pipe<FP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)
+            : cudaFuncSetAttribute(k_anyprec_pipe<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        configured[dev][di] = true;
+    }
+    if (dt == FP16) k_anyprec_pipe<FP16><<<d.n_cta + g.n_cta, kApPipeThreads, geo.smem_bytes, s>>>(g, d, f, geo);
+    else k_anyprec_pipe<BF16><<<d.n_cta + g.n_cta, kApPipeThreads, geo.smem_bytes, s>>>(g, d, f, geo);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_ap_dequant(int dt, const uint32_t* qweight, const void* lut, void* out, uint32_t N, uint32_t K,

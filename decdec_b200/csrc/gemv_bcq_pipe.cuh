@@ -5,7 +5,7 @@
 // through registers: a producer thread moves a tile of [16 k-rows x bits planes] x 128 outputs (+ the
 // alpha and q_bias rows that go with them) per stage from HBM to shared memory with three tiled TMA
 // copies (cp.async.bulk.tensor.2d, completion counted on an mbarrier), several stages ahead of the
-// eight consumer warps.  HBM latency is then covered by bytes in flight (about 29 KB per stage, up to
+// consumer warps (three groups of eight, taking stages round-robin).  HBM latency is then covered by bytes in flight (about 29 KB per stage, up to
 // 5 stages per SM) instead of by occupancy.  The tile lands densely (512-byte lines); the lanes of a
 // warp read it in a skewed order (k-row j reads the 16-byte groups (j + c) mod 8 and +4), so every
 // 128-bit shared load of a quarter warp touches eight different bank groups.
@@ -18,13 +18,19 @@
 #include "common.cuh"
 #include "gemv_bcq.cuh"
 #include <cuda.h>
+#include "dec_role.cuh"   // DD_STAMP (debug builds)
 
 namespace dd {
 
 constexpr int kPipeStageN = 128;            // outputs per stage
 constexpr int kPipeLine = 512;              // bytes of one [k-row, plane] line of a stage (128 outputs)
-constexpr int kPipeThreads = 544;           // 2 groups of 8 consumer warps + 1 producer warp
-constexpr uint32_t kPipeWaitLimit = 1u << 22;
+#ifndef DD_GROUPS
+#define DD_GROUPS 3
+#endif
+constexpr int kPipeGroups = DD_GROUPS;       // consumer groups of 8 warps, taking stages round-robin
+constexpr int kPipeThreads = kPipeGroups * 256 + 32;   // + 1 producer warp
+constexpr uint32_t kPipeWaitLimit = 1u << 20;    // polls per wait before the CTA gives up
+constexpr uint32_t kPipeSuspendNs = 100000u;     // a poll may sleep this long in hardware (wakes early on completion)
 
 struct PipeGeom {
     uint32_t stages;         // pipeline depth S
@@ -50,9 +56,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(kPipeSuspendNs) : "memory");
     return ok != 0;
 }
 // bounded wait: false if the barrier did not flip within the limit or another thread gave up
@@ -97,24 +103,39 @@ __device__ __forceinline__ void lds4f(const unsigned char* base, uint32_t elem, 
     }
 }
 
-// Shared memory: [tables 64 KB][rowsum 64 B][flags 16 B][full barriers 8x8 B][empty barriers 8x8 B][stages...]
-constexpr int kPipeHdr = (kBcqTableBytes + 64 + 16 + 64 + 64 + 127) & ~127;   // stages (TMA destinations) start 128-byte aligned
-static_assert(kPipeHdr % 128 == 0, "TMA destinations must be 128-byte aligned");
+// Shared memory.  The 64 KB of tables start at the first shared-window address that is a multiple of
+// 64 KB, so that a lookup address {entry byte, slot offset} is complete after ONE byte-permute (bits
+// 16.. of the address come from a constant byte); the pipeline stages fill the space before and after:
+//   [header 256 B: rowsum, flags, 8 full + 8 empty barriers][stages ...][tables @ 64 KB multiple][stages ...]
+constexpr int kPipeHdr = 256;
+constexpr uint32_t kPipeTblOffAssumed = 65536 - 1024;   // dynamic shared memory normally starts 1 KB into the window
+
+// stages that fit before the tables when these start `tbl_off` bytes into dynamic shared memory
+__host__ __device__ inline uint32_t pipe_stages_before(uint32_t tbl_off, uint32_t stage_bytes) {
+    return tbl_off > (uint32_t)kPipeHdr ? (tbl_off - kPipeHdr) / stage_bytes : 0u;
+}
 
 template <int DT, int BITS>
 __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const PipeGeom& geo, const PipeMaps& maps,
                               uint32_t cta, unsigned char* sm) {
     using T = typename Tr<DT>::T;
     constexpr uint32_t ESZ = (DT == FP32) ? 4u : 2u;
-    float* tbl = reinterpret_cast<float*>(sm);
-    float* rowsum = reinterpret_cast<float*>(sm + kBcqTableBytes);
-    volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(sm + kBcqTableBytes + 64);
-    unsigned* s_flag = reinterpret_cast<unsigned*>(sm + kBcqTableBytes + 64 + 4);
-    const uint32_t bar_full = smem_u32(sm + kBcqTableBytes + 80);
+    const uint32_t sm_base = smem_u32(sm);
+    const uint32_t tbl_off = (65536u - (sm_base & 65535u)) & 65535u;     // tables at a 64 KB multiple of the window
+    float* tbl = reinterpret_cast<float*>(sm + tbl_off);
+    float* rowsum = reinterpret_cast<float*>(sm);
+    volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(sm + 64);
+    unsigned* s_flag = reinterpret_cast<unsigned*>(sm + 64 + 4);
+    const uint32_t bar_full = smem_u32(sm + 80);
     const uint32_t bar_empty = bar_full + 64;
-    unsigned char* stage0 = sm + kPipeHdr;
+    const uint32_t n_before = pipe_stages_before(tbl_off, geo.stage_bytes);
+    auto stage_ptr = [&](uint32_t s) -> unsigned char* {
+        return s < n_before ? sm + kPipeHdr + (size_t)s * geo.stage_bytes
+                            : sm + tbl_off + kBcqTableBytes + (size_t)(s - n_before) * geo.stage_bytes;
+    };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    DD_STAMP(cta, 0);
     const uint32_t ks = cta % p.n_kslices;
     const uint32_t tile = cta / p.n_kslices;
     const uint32_t kbase = ks * kBcqSlice;
@@ -124,6 +145,16 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
     const uint32_t S = geo.stages;
     const uint32_t groups = kBcqSlice / p.group;      // scale groups inside the K slice
 
+    {
+        // the host sized the launch for the usual window offset; refuse to run past the allocation
+        uint32_t dyn;
+        asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+        const uint32_t after = S > n_before ? S - n_before : 0u;
+        if (tbl_off + kBcqTableBytes + after * geo.stage_bytes > dyn || (tbl_off & 127u)) {
+            if (tid == 0) atomicExch(f.err, 2u);
+            return;
+        }
+    }
     if (tid == 0) {
         *s_abort = 0u;
         for (uint32_t s = 0; s < S; ++s) {
@@ -134,18 +165,22 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
     }
     __syncthreads();
 
-    if (warp == 16) {
+    if (warp == kPipeGroups * 8) {
         // ------------------------------ producer warp (one elected lane) -------------------------
         const uint32_t tx = geo.w_bytes + geo.a_bytes + groups * kPipeStageN * ESZ;
         uint32_t issued = 0;
+#if defined(DD_EXP) && DD_EXP == 2
+        if (false) {      // compute only: nothing is streamed, consumers read whatever shared memory holds
+#else
         if (lane == 0) {
+#endif
             for (uint32_t i = 0; i < nst; ++i) {
                 const uint32_t s = i % S, use = i / S;
                 if (use > 0 && !mbar_wait(bar_empty + 8 * s, (use - 1) & 1u, s_abort)) break;
                 const uint32_t full = bar_full + 8 * s;
                 mbar_expect_tx(full, tx);
                 const uint32_t n0 = (st0 + i) * kPipeStageN;
-                const uint32_t dst = smem_u32(stage0 + (size_t)s * geo.stage_bytes);
+                const uint32_t dst = smem_u32(stage_ptr(s));
                 tma_2d_g2s(dst, &maps.w, n0, (kbase / 32) * BITS, full);
                 tma_2d_g2s(dst + geo.w_bytes, &maps.a, n0, (kbase / p.group) * BITS, full);
                 tma_2d_g2s(dst + geo.w_bytes + geo.a_bytes, &maps.b, n0, kbase / p.group, full);
@@ -164,7 +199,7 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
         // ------------------------------ consumer warps (8) ---------------------------------------
         // build the 64 subset-sum tables of the slice: slot = (krow / 8) * 32 + (krow % 8) * 4 + byte;
         // a thread fills the 32 entries whose bits 5..7 equal warp / 2
-        {
+        if (warp < 16) {
             const uint32_t slot = (warp & 1) * 32 + lane;
             const uint32_t qe = warp >> 1;
             const uint32_t krow_b = (slot >> 5) * 8 + ((slot & 31) >> 2);
@@ -187,12 +222,13 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
                 for (int l = 0; l < 8; ++l) tbl[(qe * 32 + h * 8 + l) * 64 + slot] = th + lo[l];
             }
         }
-        asm volatile("bar.sync 1, 512;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(kPipeGroups * 256) : "memory");
         if (tid < 16) {
             const uint32_t base = (tid >> 3) * 32 + (tid & 7) * 4;
             rowsum[tid] = tbl[255 * 64 + base] + tbl[255 * 64 + base + 1] + tbl[255 * 64 + base + 2] + tbl[255 * 64 + base + 3];
         }
-        asm volatile("bar.sync 1, 512;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(kPipeGroups * 256) : "memory");
+        DD_STAMP(cta, 1);
 
         // two groups of 8 warps take alternate stages.  Inside a group:
         // warp = (k half, 32-output block); lane = (k-row j, c).  Row j reads the 16-byte groups
@@ -206,10 +242,10 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
             const uint32_t byte = (s + c) & 3;
-            sel[s] = 0x6504u | (byte << 4);
-            lb[s] = (4 * j + byte) * 4;
+            sel[s] = 0x6504u | (byte << 4);                // result bytes = {lb.b0, word.byte[byte], lb.b1, lb.b2}
+            // b0 = slot offset inside a 256-byte entry row, b1 = bits 16..23 of the tables' window address
+            lb[s] = (khalf * 128 + (4 * j + byte) * 4) | (((smem_u32(tbl) >> 16) & 0xffu) << 8);
         }
-        const uint32_t tbi_s = smem_u32(tbl) + khalf * 128;
         const float sx = rowsum[krow];
         const uint32_t g = (32 * krow) / p.group;          // scale group of this lane's k-row inside the slice
         const uint32_t nA = blk * 32 + 4 * tA, nB = blk * 32 + 4 * tB;
@@ -220,10 +256,13 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
         const uint32_t r = tA & 3;
         const uint32_t n_out = blk * 32 + ((j & 4) ? 16 : 0) + 4 * r + (j & 3);
 
-        for (uint32_t i = grp; i < nst; i += 2) {
+        for (uint32_t i = grp; i < nst; i += kPipeGroups) {
             const uint32_t s = i % S;
+#if !(defined(DD_EXP) && DD_EXP == 2)
             if (!mbar_wait(bar_full + 8 * s, (i / S) & 1u, s_abort)) break;
-            const unsigned char* st = stage0 + (size_t)s * geo.stage_bytes;
+#endif
+            if (i == 0) DD_STAMP(cta, 2);
+            const unsigned char* st = stage_ptr(s);
             const unsigned char* wl = st + krow * (BITS * kPipeLine);
             const unsigned char* al = st + geo.w_bytes + (g * BITS) * (kPipeStageN * ESZ);
             const unsigned char* bl = st + geo.w_bytes + geo.a_bytes + g * (kPipeStageN * ESZ);
@@ -232,8 +271,34 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
             lds4f<DT>(bl, nB, y8 + 4);
 #pragma unroll
             for (int q = 0; q < 8; ++q) y8[q] *= sx;
+#if defined(DD_EXP) && DD_EXP == 1
+            y8[0] += __uint_as_float(*reinterpret_cast<const uint32_t*>(wl + nA * 4));   // stream only: no lookups
+#else
+#if defined(DD_VAR) && DD_VAR == 3
 #pragma unroll 1
+#else
+#pragma unroll
+#endif
             for (int pl = 0; pl < BITS; ++pl) {
+#if defined(DD_VAR) && DD_VAR == 1
+#pragma unroll 1
+                for (int hh = 0; hh < 2; ++hh) {
+                    const uint4 wv = *reinterpret_cast<const uint4*>(wl + pl * kPipeLine + (hh ? nB : nA) * 4);
+                    float a4[4];
+                    lds4f<DT>(al + pl * (kPipeStageN * ESZ), hh ? nB : nA, a4);
+                    const uint32_t wq[4] = {wv.x, wv.y, wv.z, wv.w};
+                    float v[16];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int ss = 0; ss < 4; ++ss) v[q * 4 + ss] = lds_f32(__byte_perm(wq[q], lb[ss], sel[ss]));
+                    float r4[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) r4[q] = a4[q] * ((v[q * 4] + v[q * 4 + 1]) + (v[q * 4 + 2] + v[q * 4 + 3]));
+                    if (hh) { y8[4] += r4[0]; y8[5] += r4[1]; y8[6] += r4[2]; y8[7] += r4[3]; }
+                    else { y8[0] += r4[0]; y8[1] += r4[1]; y8[2] += r4[2]; y8[3] += r4[3]; }
+                }
+#else
                 const uint4 wA = *reinterpret_cast<const uint4*>(wl + pl * kPipeLine + nA * 4);
                 const uint4 wB = *reinterpret_cast<const uint4*>(wl + pl * kPipeLine + nB * 4);
                 float a8[8];
@@ -244,13 +309,17 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
 #pragma unroll
                 for (int q = 0; q < 8; ++q)
 #pragma unroll
-                    for (int ss = 0; ss < 4; ++ss) v[q * 4 + ss] = lds_f32(tbi_s + __byte_perm(wq[q], lb[ss], sel[ss]));
+                    for (int ss = 0; ss < 4; ++ss) v[q * 4 + ss] = lds_f32(__byte_perm(wq[q], lb[ss], sel[ss]));
 #pragma unroll
                 for (int q = 0; q < 8; ++q)
                     y8[q] = fmaf(a8[q], (v[q * 4] + v[q * 4 + 1]) + (v[q * 4 + 2] + v[q * 4 + 3]), y8[q]);
+#endif
             }
+#endif
             __syncwarp();
+#if !(defined(DD_EXP) && DD_EXP == 2)
             if (lane == 0) mbar_arrive(bar_empty + 8 * s);      // all shared reads of the stage are done
+#endif
             // X = values of group r, Y = values of group r + 4; reduce over the 8 k-row lanes, halving
             float y4[4], y2[2], y1;
 #pragma unroll
@@ -276,11 +345,13 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
         }
     }
     __syncthreads();
+    DD_STAMP(cta, 3);
     if (*s_abort) {
         if (tid == 0) atomicExch(f.err, 1u);
         return;
     }
     arrive_and_finalize<DT>(f, tile, tile + 1, s_flag, kPipeThreads);
+    DD_STAMP(cta, 4);
 }
 
 }  // namespace dd

@@ -8,7 +8,7 @@ namespace dd {
 template <int DT, bool FAST3>
 __global__ void __launch_bounds__(kThreads)
 k_anyprec(const __grid_constant__ ApParams g, const __grid_constant__ DecParams d, const __grid_constant__ FinParams f) {
-    extern __shared__ __align__(16) unsigned char sm[];
+    extern __shared__ __align__(128) unsigned char sm[];
     if (blockIdx.x < d.n_cta) dec_role<DT>(d, f, blockIdx.x, sm);
     else if constexpr (FAST3) ap3_role<DT>(g, f, blockIdx.x - d.n_cta, sm);
     else apg_role<DT>(g, f, blockIdx.x - d.n_cta, sm);

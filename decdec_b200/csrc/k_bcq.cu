@@ -8,7 +8,7 @@ namespace dd {
 template <int DT, int BITS>
 __global__ void __launch_bounds__(kThreads, 2)
 k_bcq(const __grid_constant__ BcqParams g, const __grid_constant__ DecParams d, const __grid_constant__ FinParams f) {
-    extern __shared__ __align__(16) unsigned char sm[];
+    extern __shared__ __align__(128) unsigned char sm[];
     if (blockIdx.x < d.n_cta) dec_role<DT>(d, f, blockIdx.x, sm);
     else bcq_role<DT, BITS>(g, f, blockIdx.x - d.n_cta, sm);
 }
@@ -113,16 +113,19 @@ bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, in
     geo->w_bytes = 16 * bits * kPipeLine;
     geo->a_bytes = groups * bits * kPipeStageN * esz;
     geo->stage_bytes = (geo->w_bytes + geo->a_bytes + groups * kPipeStageN * esz + 127u) & ~127u;
-    const uint32_t budget = 227 * 1024 - kPipeHdr;
-    uint32_t smax = budget / geo->stage_bytes;
-    if (smax > 6) smax = 6;
+    // stages sit before and after the 64 KB table block (see gemv_bcq_pipe.cuh)
+    const uint32_t n_before = pipe_stages_before(kPipeTblOffAssumed, geo->stage_bytes);
+    const uint32_t room_after = 227 * 1024 - (kPipeTblOffAssumed + kBcqTableBytes);
+    uint32_t smax = n_before + room_after / geo->stage_bytes;
+    if (smax > 8) smax = 8;
     if (smax < 2) return false;
     const uint32_t nst_total = N / kPipeStageN;
     // one CTA (16 consumer warps) per SM; tiles sized so that the grid is at most one wave
     uint32_t per1 = 148 / n_kslices; if (per1 == 0) per1 = 1;
     geo->tile_stages = (nst_total + per1 - 1) / per1;
     geo->stages = geo->tile_stages < smax ? geo->tile_stages : smax;
-    geo->smem_bytes = kPipeHdr + geo->stages * geo->stage_bytes;
+    const uint32_t after = geo->stages > n_before ? geo->stages - n_before : 0;
+    geo->smem_bytes = kPipeTblOffAssumed + kBcqTableBytes + after * geo->stage_bytes;
     if (geo->smem_bytes < (uint32_t)DecSmem::kBytes) geo->smem_bytes = DecSmem::kBytes;
     return true;
 }
@@ -145,3 +148,8 @@ cudaError_t launch_bcq(int dt, const BcqParams& g, const DecParams& d, const Fin
 }
 
 }  // namespace dd
+#ifdef DD_PROF
+extern "C" int decdec_debug_prof_bcq(unsigned long long* out, int n) {
+    return (int)cudaMemcpyFromSymbol(out, dd::g_dd_prof, sizeof(unsigned long long) * n);
+}
+#endif

@@ -6,7 +6,7 @@ namespace dd {
 
 template <int DT>
 __global__ void __launch_bounds__(kThreads) k_dec_only(const __grid_constant__ DecParams d, const __grid_constant__ FinParams f) {
-    extern __shared__ __align__(16) unsigned char sm[];
+    extern __shared__ __align__(128) unsigned char sm[];
     dec_role<DT>(d, f, blockIdx.x, sm);
 }
 

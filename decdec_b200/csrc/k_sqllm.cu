@@ -7,7 +7,7 @@ namespace dd {
 template <int DT>
 __global__ void __launch_bounds__(kThreads)
 k_sqllm(const __grid_constant__ SqParams g, const __grid_constant__ DecParams d, const __grid_constant__ FinParams f) {
-    extern __shared__ __align__(16) unsigned char sm[];
+    extern __shared__ __align__(128) unsigned char sm[];
     if (blockIdx.x < d.n_cta) dec_role<DT>(d, f, blockIdx.x, sm);
     else sq_role<DT>(g, f, blockIdx.x - d.n_cta, sm);
 }

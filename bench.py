@@ -37,6 +37,7 @@ MODELS = {
     "llama3-70b": (80, 8192, 64, 8, 128, 28672),
 }
 BITS, GROUP = 3, 128
+NCU_TRAFFIC_RATIO = 51.72 / 51.53   # measured DRAM bytes / algorithmic bytes of k_bcq_pipe, profiles/k_bcq_pipe_*.md
 
 
 def projections(model: str, tp: int = 1, rank: int = 0):
@@ -211,10 +212,18 @@ def build_model(args, torch, ext, dev, rank, tp):
             qb = ((torch.rand(k // GROUP, n, device=dev, generator=g) - 0.5) * 0.01).half()
             q, sc, thr = host_res[name]
             cfg_on = ext.create_dec_config(ctx, args.k_chunk, q, sc, thr)
-            y = torch.zeros(1, 1, n, dtype=torch.float16, device=dev)
-            layer.append(dict(name=name, n=n, k=k, par=par, qw=qw, alpha=alpha, qb=qb, cfg=cfg_on, y=y, thr=thr))
+            layer.append(dict(name=name, n=n, k=k, par=par, qw=qw, alpha=alpha, qb=qb, cfg=cfg_on, thr=thr))
         model.append(layer)
-    return model, ctx, (rows, acts)
+    # all layer outputs live in one buffer that is cleared once per token (the entry points accumulate
+    # into their output; the reference's modules clear each output with its own kernel before every call)
+    total = sum(p["n"] for layer in model for p in layer)
+    ybuf = torch.zeros(total, dtype=torch.float16, device=dev)
+    off = 0
+    for layer in model:
+        for p in layer:
+            p["y"] = ybuf[off:off + p["n"]].view(1, 1, p["n"])
+            off += p["n"]
+    return model, ctx, (rows, acts, ybuf)
 
 
 def make_inputs(torch, model, dev, n_sets=4):
@@ -234,6 +243,87 @@ def make_inputs(torch, model, dev, n_sets=4):
     return widths, sets
 
 
+def run_micro(args):
+    """One entry point on one layer shape: `--micro KIND --n N --k K [--k-chunk C --n-tb T --iters I]`.
+    Launches rotate over enough distinct weight tensors to exceed L2 (cache-cold), are captured in a CUDA
+    graph and timed with CUDA events; prints one JSON line (us per launch, algorithmic GB/s).  Also the
+    command used for the single-kernel ncu captures under profiles/."""
+    import torch
+    import decdec_ext as ext
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    N, K, kind = args.n, args.k, args.micro
+    g = torch.Generator(device=dev).manual_seed(1)
+    wbytes = BITS * N * K / 8
+    ncopy = max(2, min(32, int(160e6 // wbytes) + 1))
+    x = [torch.randn(1, 1, K, device=dev, generator=g).half() for _ in range(8)]
+    y = torch.zeros(1, 1, N, dtype=torch.float16, device=dev)
+    ri = lambda *shape: torch.randint(-2**31, 2**31 - 1, shape, dtype=torch.int32, device=dev, generator=g)
+    cfg = None
+    if "dec" in kind:
+        gc = torch.Generator().manual_seed(2)
+        rows = torch.zeros(32 * 1024, dtype=torch.int32, device=dev)
+        acts = torch.zeros(32 * 1024, dtype=torch.float16, device=dev)
+        ctx = ext.create_dec_context(args.n_tb, rows, acts)
+        cfg = ext.create_dec_config(ctx, args.k_chunk, torch.randint(-2**31, 2**31 - 1, (K, N // 8), dtype=torch.int32, generator=gc),
+                                    (torch.rand(N, generator=gc) * 1e-3 + 1e-4).half(),
+                                    torch.sort(torch.randn(K, generator=gc).abs() * 3, descending=True).values.half())
+    if "lutgemm" in kind:
+        w = [(ri(K // 32, BITS, N), (torch.rand(K // GROUP, BITS, N, device=dev, generator=g) * 0.01).half(),
+              ((torch.rand(K // GROUP, N, device=dev, generator=g) - 0.5) * 0.01).half()) for _ in range(ncopy)]
+        hbm = gemv_bytes(N, K)
+        if kind == "lutgemm":
+            call = lambda i: ext.lutgemm_gemv(x[i % 8], y, *w[i % ncopy], BITS, GROUP)
+        else:
+            call = lambda i: ext.dec_lutgemm(cfg, x[i % 8], y, *w[i % ncopy], BITS, GROUP)
+    elif "anyprec" in kind:
+        w = [(ri(BITS, N, K // 32), (torch.randn(N, 2 ** BITS, device=dev, generator=g) * 0.02).half()) for _ in range(ncopy)]
+        hbm = BITS * N * K / 8 + N * 2 ** BITS * 2 + 2 * K + 4 * N
+        if kind == "anyprec":
+            call = lambda i: ext.anyprec_gemv(x[i % 8], y, *w[i % ncopy], BITS)
+        else:
+            call = lambda i: ext.dec_anyprec(cfg, x[i % 8], y, *w[i % ncopy], BITS)
+    elif kind == "sqllm":
+        w = [(ri(K * BITS // 32, N), (torch.randn(N, 2 ** BITS, device=dev, generator=g) * 0.02).half()) for _ in range(ncopy)]
+        hbm = BITS * N * K / 8 + N * 2 ** BITS * 2 + 2 * K + 4 * N
+        call = lambda i: ext.sqllm_gemv(x[i % 8], y, *w[i % ncopy], BITS)
+    elif kind == "dec":
+        hbm = 0
+        call = lambda i: ext.dec(cfg, x[i % 8], y)
+    else:
+        raise SystemExit(f"unknown --micro {kind}")
+    iters = args.iters
+    for i in range(min(3, iters)):
+        call(i)
+    torch.cuda.synchronize()
+    us = None
+    if iters > 3:
+        n = min(iters, 32)
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            call(0)
+            s.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=s):
+                for i in range(n):
+                    call(i)
+            gr.replay()
+            s.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(1, iters // n)
+            a.record(s)
+            for _ in range(reps):
+                gr.replay()
+            b.record(s)
+            s.synchronize()
+        us = a.elapsed_time(b) * 1e3 / (reps * n)
+    link = fetch_bytes(N, K, args.k_chunk) if "dec" in kind else 0
+    print(json.dumps({"micro": kind, "N": N, "K": K, "k_chunk": args.k_chunk if "dec" in kind else None,
+                      "n_tb": args.n_tb if "dec" in kind else None, "us_per_launch": us, "distinct_weight_sets": ncopy,
+                      "hbm_algorithmic_bytes": hbm, "hbm_gbs": (hbm / us / 1e3) if us and hbm else None,
+                      "host_link_bytes": link, "host_link_gbs": (link / us / 1e3) if us and link else None}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -242,10 +332,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="llama3-8b", choices=sorted(MODELS))
     ap.add_argument("--k-chunk", type=int, default=32)
-    ap.add_argument("--n-tb", type=int, default=int(os.environ.get("DECDEC_BENCH_NTB", "48")))
+    ap.add_argument("--n-tb", type=int, default=int(os.environ.get("DECDEC_BENCH_NTB", "96")))
     ap.add_argument("--layers", type=int, default=0, help="use fewer layers (profiling captures only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--micro", default="", help="single entry point: lutgemm | dec_lutgemm | anyprec | dec_anyprec | sqllm | dec")
+    ap.add_argument("--n", type=int, default=28672)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=200)
     args = ap.parse_args()
+    if args.micro:
+        return run_micro(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     if args.impl == "reference":
@@ -276,9 +372,9 @@ def main():
     def token(on: bool):
         """All quantized linears of one token.  Inputs come from fixed activation buffers (attention,
         norms and the element-wise glue between the linears are not part of the measured path)."""
+        _keep[2].zero_()
         for layer in model:
             for p in layer:
-                p["y"].zero_()
                 if on:
                     ext.dec_lutgemm(p["cfg"], xbuf[p["k"]], p["y"], p["qw"], p["alpha"], p["qb"], BITS, GROUP)
                 else:
@@ -382,7 +478,8 @@ def main():
             "decdec_off": {"value": 1e3 / ms_off, "unit": "tokens/s", "ms_per_step": ms_off,
                            "slowdown_on_vs_off": ms_on / ms_off},
             "roofline": {"bound": "hbm", "achieved": gemv_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gemv_gbs / hbm_peak,
-                         "traffic": None, "kernel": "k_bcq<fp16,3> (GEMV role, compensation off)", "launches_per_step": calls,
+                         # ncu capture of the w1w3 launch (profiles/): dram read+write 51.72 MB for 51.53 MB algorithmic
+                         "traffic": NCU_TRAFFIC_RATIO * hbm_bytes / calls, "kernel": "k_bcq<fp16,3> (GEMV role, compensation off)", "launches_per_step": calls,
                          "algorithmic_bytes_per_step": hbm_bytes, "peak_source": peak_src,
                          "note": "bytes of all GEMV launches of a step / event-timed duration of the step with compensation off"},
             "host_link": {"achieved": link_gbs, "unit": "GB/s", "peak_spec": 64.0, "fetched_bytes_per_step": link_bytes,

@@ -83,6 +83,14 @@ __device__ __forceinline__ uint32_t ldg_stream(const uint32_t* p) {
     return v;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start while the previous kernel of the stream is still draining.  `pdl_trigger` lets the NEXT
+// kernel's CTAs be scheduled early; `pdl_wait` blocks until the PREVIOUS kernel has completed and its
+// writes are visible - it must precede every access to data a previous kernel may have written
+// (activations, outputs, accumulator, tickets, selection buffers).  Both are no-ops for plain launches.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // explicit shared-window load (the table lookups must not degrade to generic loads)
 __device__ __forceinline__ float lds_f32(uint32_t saddr) {
     float v;

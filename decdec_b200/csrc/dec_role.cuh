@@ -293,6 +293,8 @@ template <int DT>
 __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, unsigned char* sm) {
     using T = typename Tr<DT>::T;
     if (threadIdx.x >= kThreads) return;   // launches shared with a wider GEMV role: extra warps leave
+    pdl_trigger();
+    pdl_wait();                             // everything below reads activations / writes shared state
     const uint32_t rp = cta % p.n_rowparts;
     const uint32_t cp = cta / p.n_rowparts;
     // column part = a contiguous range of output tiles

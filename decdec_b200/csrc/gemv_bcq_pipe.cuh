@@ -135,6 +135,7 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
     };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_trigger();
     DD_STAMP(cta, 0);
     const uint32_t ks = cta % p.n_kslices;
     const uint32_t tile = cta / p.n_kslices;
@@ -199,6 +200,7 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
         // ------------------------------ consumer warps (8) ---------------------------------------
         // build the 64 subset-sum tables of the slice: slot = (krow / 8) * 32 + (krow % 8) * 4 + byte;
         // a thread fills the 32 entries whose bits 5..7 equal warp / 2
+        pdl_wait();     // weights are already streaming (producer warp); activations come from earlier kernels
         if (warp < 16) {
             const uint32_t slot = (warp & 1) * 32 + lane;
             const uint32_t qe = warp >> 1;
@@ -344,6 +346,7 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
             atomicAdd(&f.acc[(st0 + i) * kPipeStageN + n_out], y1);
         }
     }
+    if (warp == kPipeGroups * 8) pdl_wait();
     __syncthreads();
     DD_STAMP(cta, 3);
     if (*s_abort) {

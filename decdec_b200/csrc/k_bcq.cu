@@ -1,5 +1,6 @@
 // Binary-coded GEMV launches (entry points `lutgemm_gemv`, `dec_lutgemm`).
 #include "internal.h"
+#include <cstdlib>
 #include "dec_role.cuh"
 #include "gemv_bcq_pipe.cuh"
 
@@ -37,6 +38,12 @@ k_bcq_pipe(const __grid_constant__ BcqParams g, const __grid_constant__ DecParam
     else bcq_pipe_role<DT, BITS>(g, f, geo, maps, blockIdx.x - d.n_cta, sm);
 }
 
+static bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("DECDEC_PDL"); v = (e && *e == '0') ? 0 : 1; }
+    return v == 1;
+}
+
 template <int DT, int BITS>
 static cudaError_t go_pipe(const BcqParams& g, const DecParams& d, const FinParams& f, const PipeGeom& geo, const PipeMaps& maps,
                            cudaStream_t s) {
@@ -48,8 +55,20 @@ static cudaError_t go_pipe(const BcqParams& g, const DecParams& d, const FinPara
         if (e != cudaSuccess) return e;
         configured[dev] = 227 * 1024;
     }
-    k_bcq_pipe<DT, BITS><<<d.n_cta + g.n_cta, kPipeThreads, geo.smem_bytes, s>>>(g, d, f, geo, maps);
-    return cudaGetLastError();
+    // programmatic dependent launch: CTAs may become resident (and prefetch weights) while the previous
+    // kernel of the stream drains; the kernel waits for it before touching activations or outputs
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(d.n_cta + g.n_cta);
+    cfg.blockDim = dim3(kPipeThreads);
+    cfg.dynamicSmemBytes = geo.smem_bytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    // (only for GEMV-only launches: with the compensation role on board the early start measured slightly slower)
+    attr[0].val.programmaticStreamSerializationAllowed = (pdl_enabled() && d.n_cta == 0) ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, k_bcq_pipe<DT, BITS>, g, d, f, geo, maps);
 }
 
 template <int DT>

@@ -479,7 +479,7 @@ def main():
                            "slowdown_on_vs_off": ms_on / ms_off},
             "roofline": {"bound": "hbm", "achieved": gemv_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gemv_gbs / hbm_peak,
                          # ncu capture of the w1w3 launch (profiles/): dram read+write 51.72 MB for 51.53 MB algorithmic
-                         "traffic": NCU_TRAFFIC_RATIO * hbm_bytes / calls, "kernel": "k_bcq<fp16,3> (GEMV role, compensation off)", "launches_per_step": calls,
+                         "traffic": NCU_TRAFFIC_RATIO * hbm_bytes / calls, "kernel": "k_bcq_pipe<fp16,3> (GEMV role, compensation off)", "launches_per_step": calls,
                          "algorithmic_bytes_per_step": hbm_bytes, "peak_source": peak_src,
                          "note": "bytes of all GEMV launches of a step / event-timed duration of the step with compensation off"},
             "host_link": {"achieved": link_gbs, "unit": "GB/s", "peak_spec": 64.0, "fetched_bytes_per_step": link_bytes,

@@ -47,6 +47,8 @@ struct FinParams {
     float* acc;            // [>= N] fp32, all zero between launches
     unsigned* tickets;     // [>= n_tiles], all zero between launches
     unsigned* err;         // device error word of the workspace (0 = fine)
+    float* acc2;           // [>= N] fp32 accumulator of the UNSCALED compensation sums (null: no compensation role)
+    const void* scales;    // [N] reordered residual scales, applied when a tile is finalized (layout [nibble][N/8])
     void* y;               // caller's output [N], accumulated into
     uint32_t N;
     uint32_t tile_units;   // outputs per tile = 32 * tile_units
@@ -98,32 +100,99 @@ __device__ __forceinline__ float lds_f32(uint32_t saddr) {
     return v;
 }
 
+// Fold accumulator entries [n0, n1) into y (single rounding) and re-zero them.  n0 is a multiple of 32.
+// Four outputs per thread with all loads issued before the first use: the finalizing CTA sits at the
+// very end of a launch, so its dependent-load round trips are not hidden by anything.
+template <int DT>
+__device__ __forceinline__ void finalize_span(const FinParams& f, uint32_t n0, uint32_t n1, uint32_t nthreads) {
+    using T = typename Tr<DT>::T;
+    T* y = reinterpret_cast<T*>(f.y);
+    const T* sc = reinterpret_cast<const T*>(f.scales);
+    const uint32_t wpr = f.N / 8;
+    const bool vec = ((f.N & 3u) == 0u) && ((reinterpret_cast<uintptr_t>(f.y) & (4u * sizeof(T) - 1u)) == 0u);
+    if (vec) {
+        for (uint32_t n = n0 + 4u * threadIdx.x; n < n1; n += 4u * nthreads) {
+            float4 v = __ldcg(reinterpret_cast<const float4*>(f.acc + n));
+            float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+            float s4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (f.acc2) {
+                // compensation sums are kept unscaled so that the scale loads sit here, beside the
+                // accumulator loads, and not on the critical path of the fetch
+                r = __ldcg(reinterpret_cast<const float4*>(f.acc2 + n));
+                const uint32_t w = n >> 3, nb = n & 7u;   // nb is 0 or 4
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s4[i] = Tr<DT>::to_f(sc[(size_t)(nb + i) * wpr + w]);
+            }
+            float yo[4];
+            if constexpr (DT == FP32) {
+                const float4 yy = *reinterpret_cast<const float4*>(y + n);
+                yo[0] = yy.x; yo[1] = yy.y; yo[2] = yy.z; yo[3] = yy.w;
+            } else {
+                const uint2 raw = *reinterpret_cast<const uint2*>(y + n);
+                const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) yo[i] = Tr<DT>::to_f(e[i]);
+            }
+            __stcg(reinterpret_cast<float4*>(f.acc + n), make_float4(0.f, 0.f, 0.f, 0.f));
+            if (f.acc2) __stcg(reinterpret_cast<float4*>(f.acc2 + n), make_float4(0.f, 0.f, 0.f, 0.f));
+            yo[0] += fmaf(r.x, s4[0], v.x);
+            yo[1] += fmaf(r.y, s4[1], v.y);
+            yo[2] += fmaf(r.z, s4[2], v.z);
+            yo[3] += fmaf(r.w, s4[3], v.w);
+            if constexpr (DT == FP32) {
+                *reinterpret_cast<float4*>(y + n) = make_float4(yo[0], yo[1], yo[2], yo[3]);
+            } else {
+                uint2 raw;
+                T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) e[i] = Tr<DT>::from_f(yo[i]);
+                *reinterpret_cast<uint2*>(y + n) = raw;
+            }
+        }
+    } else {
+        for (uint32_t n = n0 + threadIdx.x; n < n1; n += nthreads) {
+            float v = __ldcg(&f.acc[n]);
+            __stcg(&f.acc[n], 0.0f);
+            if (f.acc2) {
+                const float r = __ldcg(&f.acc2[n]);
+                __stcg(&f.acc2[n], 0.0f);
+                v = fmaf(r, Tr<DT>::to_f(sc[(size_t)(n & 7u) * wpr + (n >> 3)]), v);
+            }
+            y[n] = Tr<DT>::from_f(Tr<DT>::to_f(y[n]) + v);
+        }
+    }
+}
+
 // Arrive on tiles [t0, t1); the last arriver of a tile folds the accumulator into y.
-// Must be called by all threads of the CTA, after all its reductions into `acc` were issued.
-// `nthreads` = number of threads of the CTA that take part (threads beyond it must have exited).
+// Must be called by all threads of the CTA, after all its reductions into the accumulators were issued.
+// `nthreads` = number of threads of the CTA that take part (threads beyond it must have exited; the
+// first warp always takes part).  The tickets of up to 32 tiles are taken by one warp in parallel, so a
+// CTA that covers many tiles pays one atomic round trip, not one per tile.
 template <int DT>
 __device__ __forceinline__ void arrive_and_finalize(const FinParams& f, uint32_t t0, uint32_t t1, unsigned* s_flag,
                                                     uint32_t nthreads = kThreads) {
-    using T = typename Tr<DT>::T;
     __threadfence();
     __syncthreads();
-    for (uint32_t t = t0; t < t1; ++t) {
-        if (threadIdx.x == 0) {
-            unsigned old = atomicAdd(&f.tickets[t], 1u);
-            *s_flag = (old + 1u == f.expected) ? 1u : 0u;
+    for (uint32_t tb = t0; tb < t1; tb += 32u) {
+        if (threadIdx.x < 32u) {
+            const uint32_t t = tb + threadIdx.x;
+            bool last = false;
+            if (t < t1) last = (atomicAdd(&f.tickets[t], 1u) + 1u == f.expected);
+            const unsigned m = __ballot_sync(0xffffffffu, last);
+            if (threadIdx.x == 0) *s_flag = m;
         }
         __syncthreads();
-        if (*s_flag) {
+        unsigned m = *s_flag;
+        if (m) {
             __threadfence();
-            const uint32_t n0 = t * f.tile_units * 32u;
-            const uint32_t n1 = min(f.N, n0 + f.tile_units * 32u);
-            T* y = reinterpret_cast<T*>(f.y);
-            for (uint32_t n = n0 + threadIdx.x; n < n1; n += nthreads) {
-                float v = __ldcg(&f.acc[n]);
-                __stcg(&f.acc[n], 0.0f);
-                y[n] = Tr<DT>::from_f(Tr<DT>::to_f(y[n]) + v);
+            while (m) {
+                const uint32_t t = tb + (uint32_t)(__ffs(m) - 1);
+                m &= m - 1u;
+                const uint32_t n0 = t * f.tile_units * 32u;
+                const uint32_t n1 = min(f.N, n0 + f.tile_units * 32u);
+                finalize_span<DT>(f, n0, n1, nthreads);
+                if (threadIdx.x == 0) f.tickets[t] = 0u;
             }
-            if (threadIdx.x == 0) f.tickets[t] = 0u;
         }
         __syncthreads();
     }

@@ -206,7 +206,7 @@ __device__ __forceinline__ void dec_decode_word(uint32_t w, float a, float* acc)
     }
 }
 
-// Fetch rows srow[0..nrows) x packed columns [w0, w1) and add scale * sum into acc_g.
+// Fetch rows srow[0..nrows) x packed columns [w0, w1) and add the unscaled sums into acc_g.
 // VW = words per load (4: 16-byte loads, needs N % 32 == 0; 1: scalar fallback).
 template <int DT, int VW>
 __device__ void dec_fetch(const DecParams& p, float* acc_g, uint32_t nrows, uint32_t w0, uint32_t w1, unsigned char* sm) {
@@ -214,7 +214,6 @@ __device__ void dec_fetch(const DecParams& p, float* acc_g, uint32_t nrows, uint
     const int* srow = reinterpret_cast<const int*>(sm + DecSmem::kRow);
     const float* sact = reinterpret_cast<const float*>(sm + DecSmem::kAct);
     float* red = reinterpret_cast<float*>(sm + DecSmem::kRed);
-    const T* scales = reinterpret_cast<const T*>(p.scales);
     const uint32_t wpr = p.N / 8;  // words per residual row
     const int tid = threadIdx.x;
     constexpr uint32_t kBlockWords = 128 * VW;  // at most 128 loads wide, so at least 2 row groups
@@ -247,10 +246,12 @@ __device__ void dec_fetch(const DecParams& p, float* acc_g, uint32_t nrows, uint
                     }
 #pragma unroll
                     for (int b = 0; b < UN; ++b) {
-                        dec_decode_word(q[b].x, xa[b], a + 0);
-                        dec_decode_word(q[b].y, xa[b], a + 8);
-                        dec_decode_word(q[b].z, xa[b], a + 16);
-                        dec_decode_word(q[b].w, xa[b], a + 24);
+                        if (i0 + b * R < nrows) {      // nothing to decode for the slots beyond the last row
+                            dec_decode_word(q[b].x, xa[b], a + 0);
+                            dec_decode_word(q[b].y, xa[b], a + 8);
+                            dec_decode_word(q[b].z, xa[b], a + 16);
+                            dec_decode_word(q[b].w, xa[b], a + 24);
+                        }
                     }
                 } else {
                     uint32_t q[UN];
@@ -267,24 +268,26 @@ __device__ void dec_fetch(const DecParams& p, float* acc_g, uint32_t nrows, uint
                         }
                     }
 #pragma unroll
-                    for (int b = 0; b < UN; ++b) dec_decode_word(q[b], xa[b], a);
+                    for (int b = 0; b < UN; ++b)
+                        if (i0 + b * R < nrows) dec_decode_word(q[b], xa[b], a);
                 }
             }
         }
+        DD_STAMP(blockIdx.x, 4);
         // per-thread partials -> red[value][thread] (pitch 257: conflict-free both ways), then each
         // output sums its R row groups
 #pragma unroll
         for (int i = 0; i < VW * 8; ++i) red[i * 257 + tid] = a[i];
         __syncthreads();
+        DD_STAMP(blockIdx.x, 5);
         for (uint32_t o = tid; o < nw * 8; o += kThreads) {
             const uint32_t vv = o / (VW * 8), i = o % (VW * 8);
             float sum = 0.0f;
             for (uint32_t r = 0; r < R; ++r) sum += red[i * 257 + r * tv + vv];
-            const uint32_t n = cb * 8 + o;
-            const float sc = Tr<DT>::to_f(scales[(size_t)(n & 7u) * wpr + (n >> 3)]);
-            atomicAdd(&acc_g[n], sum * sc);
+            atomicAdd(&acc_g[cb * 8 + o], sum);      // unscaled: the scale is applied when the tile is finalized
         }
         __syncthreads();
+        DD_STAMP(blockIdx.x, 6);
     }
 }
 
@@ -317,8 +320,8 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
             dec_select_chunk<DT>(p, c, kq, cp == 0, sm);
             DD_STAMP(cta, 1);
             if (w1 > w0) {
-                if (vec) dec_fetch<DT, 4>(p, f.acc, kq, w0, w1, sm);
-                else dec_fetch<DT, 1>(p, f.acc, kq, w0, w1, sm);
+                if (vec) dec_fetch<DT, 4>(p, f.acc2, kq, w0, w1, sm);
+                else dec_fetch<DT, 1>(p, f.acc2, kq, w0, w1, sm);
             }
         }
     } else {
@@ -336,8 +339,8 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
             }
             __syncthreads();
             if (w1 > w0) {
-                if (vec) dec_fetch<DT, 4>(p, f.acc, nb, w0, w1, sm);
-                else dec_fetch<DT, 1>(p, f.acc, nb, w0, w1, sm);
+                if (vec) dec_fetch<DT, 4>(p, f.acc2, nb, w0, w1, sm);
+                else dec_fetch<DT, 1>(p, f.acc2, nb, w0, w1, sm);
             }
         }
     }

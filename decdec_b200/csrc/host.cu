@@ -39,6 +39,7 @@ struct Workspace {
     float* acc = nullptr;
     unsigned* tickets = nullptr;
     unsigned* err = nullptr;     // last word of the ticket allocation
+    float* acc2 = nullptr;       // second half of the accumulator allocation (compensation sums)
 };
 
 std::mutex g_mu;
@@ -65,9 +66,10 @@ int get_workspace(cudaStream_t stream, Workspace* out) {
         return 0;
     }
     Workspace w;
-    if (cudaMalloc(&w.acc, kAccCap * sizeof(float)) != cudaSuccess) return fail(DECDEC_E_NOMEM, "cudaMalloc(accumulator) failed");
+    if (cudaMalloc(&w.acc, 2 * kAccCap * sizeof(float)) != cudaSuccess) return fail(DECDEC_E_NOMEM, "cudaMalloc(accumulator) failed");
     if (cudaMalloc(&w.tickets, (kTicketCap + 4) * sizeof(unsigned)) != cudaSuccess) { cudaFree(w.acc); return fail(DECDEC_E_NOMEM, "cudaMalloc(tickets) failed"); }
-    DD_CUDA(cudaMemset(w.acc, 0, kAccCap * sizeof(float)));
+    DD_CUDA(cudaMemset(w.acc, 0, 2 * kAccCap * sizeof(float)));
+    w.acc2 = w.acc + kAccCap;
     DD_CUDA(cudaMemset(w.tickets, 0, (kTicketCap + 4) * sizeof(unsigned)));
     w.err = w.tickets + kTicketCap;
     DD_CUDA(cudaDeviceSynchronize());
@@ -176,6 +178,8 @@ int setup_fin(FinParams* f, const Workspace& ws, void* y, uint32_t N, uint32_t t
     f->acc = ws.acc;
     f->tickets = ws.tickets;
     f->err = ws.err;
+    f->acc2 = nullptr;          // set by the callers that add a compensation role
+    f->scales = nullptr;
     f->y = y;
     f->N = N;
     f->tile_units = tile_units;
@@ -205,6 +209,8 @@ int run_dec_only(uintptr_t cfg_h, const void* x, void* y, uint32_t K, uint32_t N
     if (int r = setup_fin(&f, ws, y, N, tile_units, 0)) return r;
     if (int r = fill_dec(c, x, fused_select, f.n_tiles, &d)) return r;
     f.expected = d.n_rowparts;
+    f.acc2 = ws.acc2;
+    f.scales = d.scales;
     DD_CUDA(launch_dec_only(dtype, d, f, s));
     return 0;
 }
@@ -257,7 +263,7 @@ int run_bcq(Config* c, const void* x, void* y, const int32_t* qw, const void* al
     memset(&d, 0, sizeof(d));
     if (c) {
         if (int r = fill_dec(c, x, true, f.n_tiles, &d)) return r;
-        if (d.n_cta) f.expected += d.n_rowparts;
+        if (d.n_cta) { f.expected += d.n_rowparts; f.acc2 = ws.acc2; f.scales = d.scales; }
     }
     if (pipe) DD_CUDA(launch_bcq_pipe(dtype, g, d, f, geo, s));
     else DD_CUDA(launch_bcq(dtype, g, d, f, s));
@@ -294,7 +300,7 @@ int run_anyprec(Config* c, const void* x, void* y, const int32_t* qw, uint32_t p
     memset(&d, 0, sizeof(d));
     if (c) {
         if (int r = fill_dec(c, x, true, f.n_tiles, &d)) return r;
-        if (d.n_cta) f.expected += d.n_rowparts;
+        if (d.n_cta) { f.expected += d.n_rowparts; f.acc2 = ws.acc2; f.scales = d.scales; }
     }
     g.direct = d.n_cta ? 0u : 1u;
     if (pipe) {
@@ -328,7 +334,7 @@ int run_sqllm(Config* c, const void* x, void* y, const int32_t* qw, const void* 
     memset(&d, 0, sizeof(d));
     if (c) {
         if (int r = fill_dec(c, x, true, f.n_tiles, &d)) return r;
-        if (d.n_cta) f.expected += d.n_rowparts;
+        if (d.n_cta) { f.expected += d.n_rowparts; f.acc2 = ws.acc2; f.scales = d.scales; }
     }
     g.direct = d.n_cta ? 0u : 1u;
     DD_CUDA(launch_sqllm(dtype, g, d, f, s));

@@ -38,10 +38,11 @@ k_bcq_pipe(const __grid_constant__ BcqParams g, const __grid_constant__ DecParam
     else bcq_pipe_role<DT, BITS>(g, f, geo, maps, blockIdx.x - d.n_cta, sm);
 }
 
-static bool pdl_enabled() {
+// DECDEC_PDL: 0 = never, 1 (default) = launches without a compensation role, 2 = every launch
+static int pdl_mode() {
     static int v = -1;
-    if (v < 0) { const char* e = getenv("DECDEC_PDL"); v = (e && *e == '0') ? 0 : 1; }
-    return v == 1;
+    if (v < 0) { const char* e = getenv("DECDEC_PDL"); v = (e && *e >= '0' && *e <= '2') ? (*e - '0') : 1; }
+    return v;
 }
 
 template <int DT, int BITS>
@@ -65,7 +66,7 @@ static cudaError_t go_pipe(const BcqParams& g, const DecParams& d, const FinPara
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     // (only for GEMV-only launches: with the compensation role on board the early start measured slightly slower)
-    attr[0].val.programmaticStreamSerializationAllowed = (pdl_enabled() && d.n_cta == 0) ? 1 : 0;
+    attr[0].val.programmaticStreamSerializationAllowed = (pdl_mode() == 2 || (pdl_mode() == 1 && d.n_cta == 0)) ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, k_bcq_pipe<DT, BITS>, g, d, f, geo, maps);

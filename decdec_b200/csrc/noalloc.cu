@@ -101,6 +101,8 @@ extern "C" int decdec_lutgemm_gemv_noalloc(const void* x, void* y, const int32_t
     f.acc = reinterpret_cast<float*>(scratch);
     f.tickets = reinterpret_cast<unsigned*>(scratch + kAccBytes);
     f.err = f.tickets + kMaxTiles;
+    f.acc2 = nullptr;       // no compensation role on this path
+    f.scales = nullptr;
     f.y = y;
     f.N = N;
     f.tile_units = tile_units;

@@ -111,42 +111,56 @@ __device__ __forceinline__ void finalize_span(const FinParams& f, uint32_t n0, u
     const uint32_t wpr = f.N / 8;
     const bool vec = ((f.N & 3u) == 0u) && ((reinterpret_cast<uintptr_t>(f.y) & (4u * sizeof(T) - 1u)) == 0u);
     if (vec) {
-        for (uint32_t n = n0 + 4u * threadIdx.x; n < n1; n += 4u * nthreads) {
-            float4 v = __ldcg(reinterpret_cast<const float4*>(f.acc + n));
-            float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-            float s4[4] = {0.f, 0.f, 0.f, 0.f};
-            if (f.acc2) {
-                // compensation sums are kept unscaled so that the scale loads sit here, beside the
-                // accumulator loads, and not on the critical path of the fetch
-                r = __ldcg(reinterpret_cast<const float4*>(f.acc2 + n));
-                const uint32_t w = n >> 3, nb = n & 7u;   // nb is 0 or 4
+        constexpr int U = 2;      // groups of four outputs per thread and pass, loads of all groups issued first
+        for (uint32_t nb = n0 + 4u * threadIdx.x; nb < n1; nb += 4u * nthreads * U) {
+            float4 v[U], r[U];
+            float s4[U][4];
+            float yo[U][4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) s4[i] = Tr<DT>::to_f(sc[(size_t)(nb + i) * wpr + w]);
+            for (int u = 0; u < U; ++u) {
+                const uint32_t n = nb + 4u * nthreads * u;
+                r[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s4[u][i] = 0.f;
+                if (n >= n1) continue;
+                v[u] = __ldcg(reinterpret_cast<const float4*>(f.acc + n));
+                if (f.acc2) {
+                    // compensation sums are kept unscaled so that the scale loads sit here, beside the
+                    // accumulator loads, and not on the critical path of the fetch
+                    r[u] = __ldcg(reinterpret_cast<const float4*>(f.acc2 + n));
+                    const uint32_t w = n >> 3, nib = n & 7u;   // nib is 0 or 4
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) s4[u][i] = Tr<DT>::to_f(sc[(size_t)(nib + i) * wpr + w]);
+                }
+                if constexpr (DT == FP32) {
+                    const float4 yy = *reinterpret_cast<const float4*>(y + n);
+                    yo[u][0] = yy.x; yo[u][1] = yy.y; yo[u][2] = yy.z; yo[u][3] = yy.w;
+                } else {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(y + n);
+                    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) yo[u][i] = Tr<DT>::to_f(e[i]);
+                }
             }
-            float yo[4];
-            if constexpr (DT == FP32) {
-                const float4 yy = *reinterpret_cast<const float4*>(y + n);
-                yo[0] = yy.x; yo[1] = yy.y; yo[2] = yy.z; yo[3] = yy.w;
-            } else {
-                const uint2 raw = *reinterpret_cast<const uint2*>(y + n);
-                const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) yo[i] = Tr<DT>::to_f(e[i]);
-            }
-            __stcg(reinterpret_cast<float4*>(f.acc + n), make_float4(0.f, 0.f, 0.f, 0.f));
-            if (f.acc2) __stcg(reinterpret_cast<float4*>(f.acc2 + n), make_float4(0.f, 0.f, 0.f, 0.f));
-            yo[0] += fmaf(r.x, s4[0], v.x);
-            yo[1] += fmaf(r.y, s4[1], v.y);
-            yo[2] += fmaf(r.z, s4[2], v.z);
-            yo[3] += fmaf(r.w, s4[3], v.w);
-            if constexpr (DT == FP32) {
-                *reinterpret_cast<float4*>(y + n) = make_float4(yo[0], yo[1], yo[2], yo[3]);
-            } else {
-                uint2 raw;
-                T* e = reinterpret_cast<T*>(&raw);
+            for (int u = 0; u < U; ++u) {
+                const uint32_t n = nb + 4u * nthreads * u;
+                if (n >= n1) continue;
+                __stcg(reinterpret_cast<float4*>(f.acc + n), make_float4(0.f, 0.f, 0.f, 0.f));
+                if (f.acc2) __stcg(reinterpret_cast<float4*>(f.acc2 + n), make_float4(0.f, 0.f, 0.f, 0.f));
+                yo[u][0] += fmaf(r[u].x, s4[u][0], v[u].x);
+                yo[u][1] += fmaf(r[u].y, s4[u][1], v[u].y);
+                yo[u][2] += fmaf(r[u].z, s4[u][2], v[u].z);
+                yo[u][3] += fmaf(r[u].w, s4[u][3], v[u].w);
+                if constexpr (DT == FP32) {
+                    *reinterpret_cast<float4*>(y + n) = make_float4(yo[u][0], yo[u][1], yo[u][2], yo[u][3]);
+                } else {
+                    uint2 raw;
+                    T* e = reinterpret_cast<T*>(&raw);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) e[i] = Tr<DT>::from_f(yo[i]);
-                *reinterpret_cast<uint2*>(y + n) = raw;
+                    for (int i = 0; i < 4; ++i) e[i] = Tr<DT>::from_f(yo[u][i]);
+                    *reinterpret_cast<uint2*>(y + n) = raw;
+                }
             }
         }
     } else {
@@ -186,12 +200,16 @@ __device__ __forceinline__ void arrive_and_finalize(const FinParams& f, uint32_t
         if (m) {
             __threadfence();
             while (m) {
-                const uint32_t t = tb + (uint32_t)(__ffs(m) - 1);
-                m &= m - 1u;
+                // a run of consecutive finished tiles is folded as one span, so all threads have work
+                const uint32_t b0 = (uint32_t)(__ffs(m) - 1);
+                const unsigned rest = ~(m >> b0);
+                const uint32_t run = rest ? (uint32_t)(__ffs(rest) - 1) : 32u - b0;
+                m = (b0 + run >= 32u) ? 0u : (m & (0xffffffffu << (b0 + run)));
+                const uint32_t t = tb + b0;
                 const uint32_t n0 = t * f.tile_units * 32u;
-                const uint32_t n1 = min(f.N, n0 + f.tile_units * 32u);
+                const uint32_t n1 = min(f.N, n0 + run * f.tile_units * 32u);
                 finalize_span<DT>(f, n0, n1, nthreads);
-                if (threadIdx.x == 0) f.tickets[t] = 0u;
+                if (threadIdx.x < run) f.tickets[t + threadIdx.x] = 0u;
             }
         }
         __syncthreads();

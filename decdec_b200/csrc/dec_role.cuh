@@ -32,6 +32,10 @@ __device__ __forceinline__ void dd_stamp(uint32_t cta, int slot) {
 #define DD_STAMP(cta, slot)
 #endif
 
+// Barrier of the first kThreads threads of the CTA (selection and the grouped fetch run on those; a launch
+// shared with a wider GEMV role has more threads, which only join the CTA-wide phases).
+__device__ __forceinline__ void dec_bar() { asm volatile("bar.sync 2, %0;" :: "n"(kThreads) : "memory"); }
+
 // Dynamic shared memory carve-up of the DEC role (bytes).
 struct DecSmem {
     static constexpr int kXf = 0;                         // float  xf[1024]     signed activations of the chunk
@@ -61,7 +65,7 @@ __device__ __forceinline__ float bucket_floor(float a_f, float b_f, int L) {
     return Tr<DT>::to_f(Tr<DT>::from_f(t));
 }
 
-// Select kq rows of chunk `c` into srow/sact (shared); all threads participate.
+// Select kq rows of chunk `c` into srow/sact (shared); the first kThreads threads participate.
 //
 // Rule (same set as the reference, dec.cu:117-177, made reproducible):
 //   bucket(e)  = the lowest L with floor[L] <= |x_e|   (NaN and inf belong to no bucket);
@@ -93,7 +97,7 @@ __device__ void dec_select_chunk(const DecParams& p, uint32_t c, uint32_t kq, bo
         floors[tid] = bucket_floor<DT>(p.thr_a, p.thr_b, tid);
         cum[tid] = 0u;
     }
-    __syncthreads();
+    dec_bar();
 
     // G bit L = (|x| >= floor[L]); bucket = lowest set bit
     uint32_t G[4] = {0u, 0u, 0u, 0u};
@@ -140,7 +144,7 @@ __device__ void dec_select_chunk(const DecParams& p, uint32_t c, uint32_t kq, bo
         below += __popc(v);
     }
     atomicAdd(&cum[lane], below);
-    __syncthreads();
+    dec_bar();
 
     // boundary bucket: first L with cum[L] >= kq (32 if the chunk has fewer than kq finite values)
     const uint32_t cl = cum[lane];
@@ -157,7 +161,7 @@ __device__ void dec_select_chunk(const DecParams& p, uint32_t c, uint32_t kq, bo
         balB[it] = __ballot_sync(0xffffffffu, bk[it] == Lb && Lb < 32);
         if (lane == 0) cnt[it * 8 + warp] = __popc(balA[it]) | (__popc(balB[it]) << 16);
     }
-    __syncthreads();
+    dec_bar();
     uint32_t inc = cnt[lane];
     const uint32_t own = inc;
 #pragma unroll
@@ -194,7 +198,7 @@ __device__ void dec_select_chunk(const DecParams& p, uint32_t c, uint32_t kq, bo
         sact[r] = 0.0f;
         if (publish) { g_rows[r] = (int)s; g_acts[r] = Tr<DT>::from_f(0.0f); }
     }
-    __syncthreads();
+    dec_bar();
 }
 
 __device__ __forceinline__ void dec_decode_word(uint32_t w, float a, float* acc) {
@@ -207,6 +211,9 @@ __device__ __forceinline__ void dec_decode_word(uint32_t w, float a, float* acc)
 }
 
 // Fetch rows srow[0..nrows) x packed columns [w0, w1) and add the unscaled sums into acc_g.
+// Grouped form, run by the first kThreads threads: a block of columns is covered by R row groups of
+// threads whose partial sums meet in shared memory - the right shape when the CTA's column range is
+// narrow (many compensation CTAs).
 // VW = words per load (4: 16-byte loads, needs N % 32 == 0; 1: scalar fallback).
 template <int DT, int VW>
 __device__ void dec_fetch(const DecParams& p, float* acc_g, uint32_t nrows, uint32_t w0, uint32_t w1, unsigned char* sm) {
@@ -278,7 +285,7 @@ __device__ void dec_fetch(const DecParams& p, float* acc_g, uint32_t nrows, uint
         // output sums its R row groups
 #pragma unroll
         for (int i = 0; i < VW * 8; ++i) red[i * 257 + tid] = a[i];
-        __syncthreads();
+        dec_bar();
         DD_STAMP(blockIdx.x, 5);
         for (uint32_t o = tid; o < nw * 8; o += kThreads) {
             const uint32_t vv = o / (VW * 8), i = o % (VW * 8);
@@ -286,16 +293,79 @@ __device__ void dec_fetch(const DecParams& p, float* acc_g, uint32_t nrows, uint
             for (uint32_t r = 0; r < R; ++r) sum += red[i * 257 + r * tv + vv];
             atomicAdd(&acc_g[cb * 8 + o], sum);      // unscaled: the scale is applied when the tile is finalized
         }
-        __syncthreads();
+        dec_bar();
         DD_STAMP(blockIdx.x, 6);
     }
 }
 
-// One DEC CTA.  `cta` in [0, p.n_cta).
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// Direct form, run by all `nthr` threads of the CTA: a thread owns a 16-byte column vector (32 outputs) and
+// every R-th selected row of it (R = thread groups that fit beside each other on the column range), keeps
+// up to eight row loads in flight, and adds its sums with 16-byte vector reductions.  No shared-memory
+// exchange and no barrier, so warps drift apart and keep the link busy; the right shape when the CTA's
+// column range is wide (few compensation CTAs).  The 32 sums are formed in two halves of 16 so that the
+// eight loaded vectors stay in registers under the register cap of the widest GEMV launch.
+// Needs N % 32 == 0 (w0, w1 are then multiples of 4 words).
+template <int DT>
+__device__ void dec_fetch_direct(const DecParams& p, float* acc_g, uint32_t nrows, uint32_t w0, uint32_t w1,
+                                 const unsigned char* sm, uint32_t nthr) {
+    const int* srow = reinterpret_cast<const int*>(sm + DecSmem::kRow);
+    const float* sact = reinterpret_cast<const float*>(sm + DecSmem::kAct);
+    const uint32_t wpr = p.N / 8;
+    const uint32_t nvec = (w1 - w0) / 4u;
+    uint32_t R = nthr / nvec;                       // row groups side by side (1..16 by the caller's choice of form)
+    if (R == 0) R = 1;
+    // R == 1: threads stride over the column vectors; R > 1: one sweep, thread -> (vector, row group)
+    const uint32_t stride = R > 1 ? nvec * R : nthr;
+    constexpr int UN = 8;
+    for (uint32_t t = threadIdx.x; t < nvec * R; t += stride) {
+        const uint32_t v = t % nvec;
+        const uint32_t rg = t / nvec;
+        const uint32_t col = w0 + 4u * v;
+        float* dst = acc_g + (size_t)col * 8;
+        for (uint32_t i0 = rg; i0 < nrows; i0 += R * UN) {
+            uint4 q[UN];
+            float xa[UN];
+#pragma unroll
+            for (int b = 0; b < UN; ++b) {
+                const uint32_t i = i0 + b * R;
+                if (i < nrows) {
+                    q[b] = ldg_stream(reinterpret_cast<const uint4*>(p.cheat + (size_t)srow[i] * wpr + col));
+                    xa[b] = sact[i];
+                } else {
+                    q[b] = make_uint4(0, 0, 0, 0);
+                    xa[b] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float a[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) a[i] = 0.0f;
+#pragma unroll
+                for (int b = 0; b < UN; ++b) {
+                    if (i0 + b * R < nrows) {
+                        dec_decode_word(h ? q[b].z : q[b].x, xa[b], a + 0);
+                        dec_decode_word(h ? q[b].w : q[b].y, xa[b], a + 8);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    red_add_v4(dst + 16 * h + 4 * j, a[4 * j], a[4 * j + 1], a[4 * j + 2], a[4 * j + 3]);
+            }
+        }
+    }
+}
+
+// One DEC CTA.  `cta` in [0, p.n_cta).  Called by all threads of the CTA (blockDim.x >= kThreads).
 template <int DT>
 __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, unsigned char* sm) {
     using T = typename Tr<DT>::T;
-    if (threadIdx.x >= kThreads) return;   // launches shared with a wider GEMV role: extra warps leave
+    const uint32_t nthr = blockDim.x;
+    const bool first = threadIdx.x < kThreads;
     pdl_trigger();
     pdl_wait();                             // everything below reads activations / writes shared state
     const uint32_t rp = cta % p.n_rowparts;
@@ -307,6 +377,8 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
     const uint32_t w0 = min(wpr, t0 * f.tile_units * 4u);
     const uint32_t w1 = min(wpr, t1 * f.tile_units * 4u);
     const bool vec = (p.N % 32u) == 0u;
+    // wide column range: at most sixteen thread groups share a column vector
+    const bool direct = vec && (w1 - w0) * 4u >= nthr;
     int* srow = reinterpret_cast<int*>(sm + DecSmem::kRow);
     float* sact = reinterpret_cast<float*>(sm + DecSmem::kAct);
     DD_STAMP(cta, 0);
@@ -317,12 +389,17 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
             const uint32_t len = min((uint32_t)kChunk, p.K - c * kChunk);
             const uint32_t kq = p.k_chunk * len / kChunk;
             if (kq == 0) continue;
-            dec_select_chunk<DT>(p, c, kq, cp == 0, sm);
+            if (first) dec_select_chunk<DT>(p, c, kq, cp == 0, sm);
+            __syncthreads();
             DD_STAMP(cta, 1);
             if (w1 > w0) {
-                if (vec) dec_fetch<DT, 4>(p, f.acc2, kq, w0, w1, sm);
-                else dec_fetch<DT, 1>(p, f.acc2, kq, w0, w1, sm);
+                if (direct) dec_fetch_direct<DT>(p, f.acc2, kq, w0, w1, sm, nthr);
+                else if (first) {
+                    if (vec) dec_fetch<DT, 4>(p, f.acc2, kq, w0, w1, sm);
+                    else dec_fetch<DT, 1>(p, f.acc2, kq, w0, w1, sm);
+                }
             }
+            __syncthreads();                // the next chunk's selection overwrites srow/sact
         }
     } else {
         // rows supplied by the caller (context buffer); activation gathered as x[row] (dec.cu:346)
@@ -331,7 +408,7 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
         const uint32_t r1 = (uint32_t)(((uint64_t)(rp + 1) * p.k_total) / p.n_rowparts);
         for (uint32_t b0 = r0; b0 < r1; b0 += kChunk) {
             const uint32_t nb = min((uint32_t)kChunk, r1 - b0);
-            for (uint32_t i = threadIdx.x; i < nb; i += kThreads) {
+            for (uint32_t i = threadIdx.x; i < nb; i += nthr) {
                 const int row = p.sel_rows[b0 + i];
                 const bool ok = row >= 0 && (uint32_t)row < p.K;   // out-of-range rows contribute nothing
                 srow[i] = ok ? row : 0;
@@ -339,13 +416,17 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
             }
             __syncthreads();
             if (w1 > w0) {
-                if (vec) dec_fetch<DT, 4>(p, f.acc2, nb, w0, w1, sm);
-                else dec_fetch<DT, 1>(p, f.acc2, nb, w0, w1, sm);
+                if (direct) dec_fetch_direct<DT>(p, f.acc2, nb, w0, w1, sm, nthr);
+                else if (first) {
+                    if (vec) dec_fetch<DT, 4>(p, f.acc2, nb, w0, w1, sm);
+                    else dec_fetch<DT, 1>(p, f.acc2, nb, w0, w1, sm);
+                }
             }
+            __syncthreads();
         }
     }
     DD_STAMP(cta, 2);
-    arrive_and_finalize<DT>(f, t0, t1, reinterpret_cast<unsigned*>(sm + DecSmem::kFlag));
+    arrive_and_finalize<DT>(f, t0, t1, reinterpret_cast<unsigned*>(sm + DecSmem::kFlag), nthr);
     DD_STAMP(cta, 3);
 }
 

@@ -136,7 +136,7 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     pdl_trigger();
-    DD_STAMP(cta, 0);
+    DD_STAMP(cta + 256, 0);
     const uint32_t ks = cta % p.n_kslices;
     const uint32_t tile = cta / p.n_kslices;
     const uint32_t kbase = ks * kBcqSlice;
@@ -230,7 +230,7 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
             rowsum[tid] = tbl[255 * 64 + base] + tbl[255 * 64 + base + 1] + tbl[255 * 64 + base + 2] + tbl[255 * 64 + base + 3];
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kPipeGroups * 256) : "memory");
-        DD_STAMP(cta, 1);
+        DD_STAMP(cta + 256, 1);
 
         // two groups of 8 warps take alternate stages.  Inside a group:
         // warp = (k half, 32-output block); lane = (k-row j, c).  Row j reads the 16-byte groups
@@ -263,7 +263,7 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
 #if !(defined(DD_EXP) && DD_EXP == 2)
             if (!mbar_wait(bar_full + 8 * s, (i / S) & 1u, s_abort)) break;
 #endif
-            if (i == 0) DD_STAMP(cta, 2);
+            if (i == 0) DD_STAMP(cta + 256, 2);
             const unsigned char* st = stage_ptr(s);
             const unsigned char* wl = st + krow * (BITS * kPipeLine);
             const unsigned char* al = st + geo.w_bytes + (g * BITS) * (kPipeStageN * ESZ);
@@ -348,13 +348,13 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
     }
     if (warp == kPipeGroups * 8) pdl_wait();
     __syncthreads();
-    DD_STAMP(cta, 3);
+    DD_STAMP(cta + 256, 3);
     if (*s_abort) {
         if (tid == 0) atomicExch(f.err, 1u);
         return;
     }
     arrive_and_finalize<DT>(f, tile, tile + 1, s_flag, kPipeThreads);
-    DD_STAMP(cta, 4);
+    DD_STAMP(cta + 256, 4);
 }
 
 }  // namespace dd

@@ -157,6 +157,17 @@ int fill_dec(const Config* c, const void* x, bool fused_select, uint32_t n_tiles
     return 0;
 }
 
+// SMs left to the GEMV thread blocks of a fused launch.  A few compensation thread blocks take their SMs
+// out of the GEMV's single wave (the GEMV grid shrinks accordingly); many of them mean the launch is bound
+// by the host link anyway, and the GEMV keeps its full grid and runs in the gaps.
+uint32_t gemv_sm_budget(const Config* c, bool fused_select) {
+    if (!c) return 148;
+    DecParams d;
+    memset(&d, 0, sizeof(d));
+    dec_geometry(c, fused_select, 1u << 20, &d);
+    return d.n_cta <= 40 ? 148 - d.n_cta : 148;
+}
+
 int check_cfg_call(const Config* c, const void* x, void* y, uint32_t K, uint32_t N, int dtype) {
     if (!c) return fail(DECDEC_E_INVALID, "null DECConfig handle");
     if (!x || !y) return fail(DECDEC_E_INVALID, "null input/output pointer");
@@ -250,7 +261,7 @@ int run_bcq(Config* c, const void* x, void* y, const int32_t* qw, const void* al
     tile_units = cdiv(tile_units, 8) * 8;
     tile_units = env_u32("DECDEC_BCQ_TILE_UNITS", tile_units);
     PipeGeom geo;
-    const bool pipe = env_u32("DECDEC_BCQ_PIPE", 1) && bcq_pipe_geometry(N, K, g.bits, g.group, dtype, g.n_kslices, &geo);
+    const bool pipe = env_u32("DECDEC_BCQ_PIPE", 1) && bcq_pipe_geometry(N, K, g.bits, g.group, dtype, g.n_kslices, &geo, gemv_sm_budget(c, true));
     FinParams f;
     if (pipe) {
         tile_units = geo.tile_stages * (kPipeStageN / 32);
@@ -291,7 +302,7 @@ int run_anyprec(Config* c, const void* x, void* y, const int32_t* qw, uint32_t p
     uint32_t tile_units = cdiv(units, target);
     tile_units = env_u32("DECDEC_AP_TILE_UNITS", tile_units);
     ApPipeGeom pgeo;
-    const bool pipe = env_u32("DECDEC_AP_PIPE", 1) && anyprec_pipe_geometry(N, K, g.bits, &pgeo);
+    const bool pipe = env_u32("DECDEC_AP_PIPE", 1) && anyprec_pipe_geometry(N, K, g.bits, &pgeo, gemv_sm_budget(c, true));
     if (pipe) tile_units = pgeo.rows_per_cta / 32;
     FinParams f;
     if (int r = setup_fin(&f, ws, y, N, tile_units, 1)) return r;

@@ -12,10 +12,11 @@ namespace dd {
 // Each launcher starts ONE grid: blocks [0, d.n_cta) run the compensation role, the rest the GEMV.
 cudaError_t launch_dec_only(int dt, const DecParams& d, const FinParams& f, cudaStream_t s);
 cudaError_t launch_bcq(int dt, const BcqParams& g, const DecParams& d, const FinParams& f, cudaStream_t s);
-bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, int dt, uint32_t n_kslices, PipeGeom* geo);
+bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, int dt, uint32_t n_kslices, PipeGeom* geo,
+                       uint32_t sm_budget = 148);   // SMs the GEMV thread blocks may fill in one wave
 cudaError_t launch_bcq_pipe(int dt, const BcqParams& g, const DecParams& d, const FinParams& f, const PipeGeom& geo, cudaStream_t s);
 cudaError_t launch_anyprec(int dt, const ApParams& g, const DecParams& d, const FinParams& f, cudaStream_t s);
-bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* geo);
+bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* geo, uint32_t sm_budget = 148);
 cudaError_t launch_anyprec_pipe(int dt, const ApParams& g, const DecParams& d, const FinParams& f, const ApPipeGeom& geo, cudaStream_t s);
 cudaError_t launch_sqllm(int dt, const SqParams& g, const DecParams& d, const FinParams& f, cudaStream_t s);
 cudaError_t launch_ap_dequant(int dt, const uint32_t* qweight, const void* lut, void* out, uint32_t N, uint32_t K,

@@ -51,7 +51,7 @@ k_anyprec_pipe(const __grid_constant__ ApParams g, const __grid_constant__ DecPa
 }
 
 // Stage geometry of the pipelined 3-bit kernel; false if the shape is not eligible.
-bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* geo) {
+bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* geo, uint32_t sm_budget) {
     if (bits != 3 || K % 128u || K > 32768u || N == 0) return false;
     const uint32_t rowbytes = K / 8;
     geo->segs = (K + 4095) / 4096;
@@ -65,7 +65,8 @@ bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* ge
     uint32_t smax = budget / geo->stage_bytes;
     if (smax > 8) smax = 8;
     if (smax < 2) return false;
-    uint32_t rows = (N + 147) / 148;
+    if (sm_budget == 0) sm_budget = 1;
+    uint32_t rows = (N + sm_budget - 1) / sm_budget;
     rows = ((rows + 31) / 32) * 32;
     geo->rows_per_cta = rows;
     const uint32_t nst = rows / R;

@@ -38,10 +38,10 @@ k_bcq_pipe(const __grid_constant__ BcqParams g, const __grid_constant__ DecParam
     else bcq_pipe_role<DT, BITS>(g, f, geo, maps, blockIdx.x - d.n_cta, sm);
 }
 
-// DECDEC_PDL: 0 = never, 1 (default) = launches without a compensation role, 2 = every launch
+// DECDEC_PDL: 0 = never, 1 = launches without a compensation role, 2 (default) = every launch
 static int pdl_mode() {
     static int v = -1;
-    if (v < 0) { const char* e = getenv("DECDEC_PDL"); v = (e && *e >= '0' && *e <= '2') ? (*e - '0') : 1; }
+    if (v < 0) { const char* e = getenv("DECDEC_PDL"); v = (e && *e >= '0' && *e <= '2') ? (*e - '0') : 2; }
     return v;
 }
 
@@ -65,7 +65,6 @@ static cudaError_t go_pipe(const BcqParams& g, const DecParams& d, const FinPara
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    // (only for GEMV-only launches: with the compensation role on board the early start measured slightly slower)
     attr[0].val.programmaticStreamSerializationAllowed = (pdl_mode() == 2 || (pdl_mode() == 1 && d.n_cta == 0)) ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
@@ -125,7 +124,8 @@ cudaError_t launch_bcq_pipe(int dt, const BcqParams& g, const DecParams& d, cons
 }
 
 // Stage geometry of the pipelined kernel; returns false if the shape is not eligible.
-bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, int dt, uint32_t n_kslices, PipeGeom* geo) {
+bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, int dt, uint32_t n_kslices, PipeGeom* geo,
+                       uint32_t sm_budget) {
     if (N % kPipeStageN || K % kBcqSlice || bits < 2 || bits > 4) return false;
     if (group < 32 || group > (uint32_t)kBcqSlice || kBcqSlice % group) return false;
     const uint32_t esz = dt == FP32 ? 4 : 2;
@@ -141,7 +141,7 @@ bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, in
     if (smax < 2) return false;
     const uint32_t nst_total = N / kPipeStageN;
     // one CTA (16 consumer warps) per SM; tiles sized so that the grid is at most one wave
-    uint32_t per1 = 148 / n_kslices; if (per1 == 0) per1 = 1;
+    uint32_t per1 = sm_budget / n_kslices; if (per1 == 0) per1 = 1;
     geo->tile_stages = (nst_total + per1 - 1) / per1;
     geo->stages = geo->tile_stages < smax ? geo->tile_stages : smax;
     const uint32_t after = geo->stages > n_before ? geo->stages - n_before : 0;

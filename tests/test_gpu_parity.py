@@ -251,6 +251,46 @@ def test_dec_lutgemm_config0(ops):
     assert np.linalg.norm(P.to_np(y).reshape(-1) - full) < np.linalg.norm(base - full)
 
 
+@pytest.mark.parametrize("entry", ["dec", "dec_lutgemm", "dec_anyprec"])
+@pytest.mark.parametrize("n_tb,k_chunk", [
+    (1, 1), (1, 9), (2, 5), (4, 3), (4, 17), (8, 4), (8, 32), (12, 7), (16, 2), (24, 12), (48, 1), (96, 32), (148, 6),
+])
+def test_compensation_geometry_sweep(ops, entry, n_tb, k_chunk):
+    """Few wide compensation thread blocks (direct fetch: vector reductions, row groups, several load batches)
+    through many narrow ones (grouped fetch), alone and fused into both pipelined GEMVs: same result."""
+    N, K = 4096, 3072
+    cs, rs = P.random_residual(N, K, seed=61)
+    thr = P.make_thresholds(K)
+    x = P.make_activation(K, seed=62)
+    ctx, rows, acts = _ctx(ops, n_tb, 32 * 1024, "fp16")
+    cfg = ops.create_dec_config(ctx, k_chunk, cs, rs, thr)
+    y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+    exp_rows, exp_acts, _ = P.expected_selection(x, thr, k_chunk, "fp16")
+    delta = ofw.dec_delta(P.to_np(x), exp_rows, cs.numpy(), P.to_np(rs), exp_acts)
+    if entry == "dec":
+        ops.dec(cfg, x.cuda(), y)
+        ref = delta
+    elif entry == "dec_lutgemm":
+        L = P.bcq_layer(N, K, 3, 128, seed=63)
+        ops.dec_lutgemm(cfg, x.cuda(), y, L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda(), 3, 128)
+        ref = ofw.layer_output(L["w_hat"], P.to_np(x), None, delta)
+    else:
+        L = P.lut_layer(N, K, 3, seed=64)
+        ops.dec_anyprec(cfg, x.cuda(), y, L["qweight"].cuda(), L["lut"].cuda(), 3)
+        ref = ofw.layer_output(L["w_hat"], P.to_np(x), None, delta)
+    torch.cuda.synchronize()
+    k = k_chunk * K // 1024
+    assert np.array_equal(rows[:k].cpu().numpy(), exp_rows)
+    _assert_close(y, ref, "fp16", f"{entry} n_tb={n_tb} k_chunk={k_chunk}")
+    # a second call accumulates onto y again: the workspace was left clean by the first
+    y2 = torch.zeros_like(y)
+    if entry == "dec":
+        ops.dec(cfg, x.cuda(), y2)
+        torch.cuda.synchronize()
+        _assert_close(y2, ref, "fp16", f"{entry} second call")
+    ops.destroy_dec_config(cfg)
+
+
 @pytest.mark.parametrize("k_chunk", [0, 8, 16, 32, 64])
 def test_dec_anyprec_config1_sweep(ops, k_chunk):
     """BASELINE config 1 (k/v projection shape 4096 -> 1024), 3-bit LUT, k_chunk sweep."""

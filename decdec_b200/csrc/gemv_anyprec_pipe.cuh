@@ -47,6 +47,7 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
     const uint32_t nst = (r1 - r0 + R - 1) / R;
     const uint32_t lut_off = 3 * R * rowbytes;          // LUT rows sit after the three plane runs
 
+    pdl_trigger();
     if (tid == 0) {
         *s_abort = 0u;
         for (uint32_t s = 0; s < S; ++s) {
@@ -87,6 +88,7 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
         }
     } else {
         // ------------------------------ consumers ----------------------------------------------
+        pdl_wait();     // weights are already streaming (producer warp); activations come from earlier kernels
         const T* x = reinterpret_cast<const T*>(p.x);
         for (uint32_t k = tid; k < p.K; k += 512) sx[(k & ~7u) | ap_perm(k & 7u)] = x[k];
         asm volatile("bar.sync 1, 512;" ::: "memory");
@@ -166,6 +168,7 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
             if (lane == 0 && has_item && n < r1) atomicAdd(&f.acc[n], facc);
         }
     }
+    if (warp == 16) pdl_wait();     // the producer warp touches the accumulator and y only from here on
     __syncthreads();
     if (*s_abort) {
         if (tid == 0) atomicExch(f.err, 1u);

@@ -45,32 +45,75 @@ __device__ void sq_role(const SqParams& p, const FinParams& f, uint32_t cta, uns
     const uint32_t ngroups = p.K / 32;                 // 32-channel groups
     const uint32_t g0 = (uint32_t)(((uint64_t)warp * ngroups) / 8), g1 = (uint32_t)(((uint64_t)(warp + 1) * ngroups) / 8);
     const uint32_t* col = p.qweight + n;
+    // Word rows are fetched for several 32-channel groups at once (all loads before the first use): a warp
+    // then has 1.5-2 KB in flight instead of 384-512 bytes, which is what hides the DRAM latency here.
+    constexpr uint32_t GB = 4;                         // groups per batch
+    const unsigned char* lbase = reinterpret_cast<const unsigned char*>(slut + lane);   // + code * 128
+    auto lut_at = [&](uint32_t byte_off) { return *reinterpret_cast<const float*>(lbase + byte_off); };
     if (p.bits == 4) {
-        for (uint32_t g = g0; g < g1; ++g) {
+        auto consume = [&](const uint32_t* w, const float* xg) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 xa = *reinterpret_cast<const float4*>(xg + 8 * i);
+                const float4 xb = *reinterpret_cast<const float4*>(xg + 8 * i + 4);
+                const float xs[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    // code * 128 taken straight out of the word: bits [4c, 4c+4) moved to bit 7
+                    const uint32_t off = (4 * c >= 7 ? (w[i] >> (4 * c - 7)) : (w[i] << (7 - 4 * c))) & 0x780u;
+                    acc = fmaf(lut_at(off), xs[c], acc);
+                }
+            }
+        };
+        uint32_t g = g0;
+        for (; g + GB <= g1; g += GB) {
+            uint32_t w[GB][4];
+#pragma unroll
+            for (uint32_t b = 0; b < GB; ++b)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) w[b][i] = nv ? ldg_stream(col + (size_t)(4 * (g + b) + i) * p.N) : 0u;
+#pragma unroll
+            for (uint32_t b = 0; b < GB; ++b) consume(w[b], sx + 32 * (g + b));
+        }
+        for (; g < g1; ++g) {
             uint32_t w[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) w[i] = nv ? ldg_stream(col + (size_t)(4 * g + i) * p.N) : 0u;
-            const float* xg = sx + 32 * g;
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int c = 0; c < 8; ++c) acc = fmaf(slut[((w[i] >> (4 * c)) & 15u) * 32 + lane], xg[8 * i + c], acc);
+            consume(w, sx + 32 * g);
         }
     } else {
-        for (uint32_t g = g0; g < g1; ++g) {
+        auto consume = [&](uint32_t w0, uint32_t w1, uint32_t w2, const float* xg) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 xv = *reinterpret_cast<const float4*>(xg + 4 * q);
+                const float xs[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c = 4 * q + j, bit = 3 * c;          // code c sits at bits [3c, 3c+3) of the 96-bit string
+                    // 32-bit window that starts at `bit` (funnel shift over the word pair that holds it)
+                    uint32_t v;
+                    if (bit < 32) v = __funnelshift_r(w0, w1, bit);
+                    else if (bit < 64) v = __funnelshift_r(w1, w2, bit - 32);
+                    else v = w2 >> (bit - 64);
+                    acc = fmaf(lut_at((v & 7u) << 7), xs[j], acc);
+                }
+            }
+        };
+        uint32_t g = g0;
+        for (; g + GB <= g1; g += GB) {
+            uint32_t w[GB][3];
+#pragma unroll
+            for (uint32_t b = 0; b < GB; ++b)
+#pragma unroll
+                for (int i = 0; i < 3; ++i) w[b][i] = nv ? ldg_stream(col + (size_t)(3 * (g + b) + i) * p.N) : 0u;
+#pragma unroll
+            for (uint32_t b = 0; b < GB; ++b) consume(w[b][0], w[b][1], w[b][2], sx + 32 * (g + b));
+        }
+        for (; g < g1; ++g) {
             const uint32_t w0 = nv ? ldg_stream(col + (size_t)(3 * g) * p.N) : 0u;
             const uint32_t w1 = nv ? ldg_stream(col + (size_t)(3 * g + 1) * p.N) : 0u;
             const uint32_t w2 = nv ? ldg_stream(col + (size_t)(3 * g + 2) * p.N) : 0u;
-            const unsigned long long lo = (unsigned long long)w0 | ((unsigned long long)w1 << 32);
-            const float* xg = sx + 32 * g;
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                uint32_t code;
-                if (3 * c + 3 <= 64) code = (uint32_t)(lo >> (3 * c)) & 7u;
-                else if (3 * c >= 64) code = (w2 >> (3 * c - 64)) & 7u;
-                else code = ((uint32_t)(lo >> (3 * c)) | (w2 << (64 - 3 * c))) & 7u;
-                acc = fmaf(slut[code * 32 + lane], xg[c], acc);
-            }
+            consume(w0, w1, w2, sx + 32 * g);
         }
     }
     part[warp * 32 + lane] = acc;

@@ -1,5 +1,6 @@
 // Any-precision launches (entry points `anyprec_gemv`, `dec_anyprec`, `anyprec_dequant`).
 #include "internal.h"
+#include <cstdlib>
 #include "dec_role.cuh"
 #include "gemv_anyprec_pipe.cuh"
 
@@ -88,9 +89,21 @@ cudaError_t launch_anyprec_pipe(int dt, const ApParams& g, const DecParams& d, c
         if (e != cudaSuccess) return e;
         configured[dev][di] = true;
     }
-    if (dt == FP16) k_anyprec_pipe<FP16><<<d.n_cta + g.n_cta, kApPipeThreads, geo.smem_bytes, s>>>(g, d, f, geo);
-    else k_anyprec_pipe<BF16><<<d.n_cta + g.n_cta, kApPipeThreads, geo.smem_bytes, s>>>(g, d, f, geo);
-    return cudaGetLastError();
+    // programmatic dependent launch: thread blocks may become resident (and prefetch weights) while the
+    // previous kernel of the stream drains; the kernel waits for it before touching activations or outputs
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(d.n_cta + g.n_cta);
+    cfg.blockDim = dim3(kApPipeThreads);
+    cfg.dynamicSmemBytes = geo.smem_bytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    const char* e = getenv("DECDEC_PDL");
+    attr[0].val.programmaticStreamSerializationAllowed = (e && *e == '0') ? 0 : 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (dt == FP16) return cudaLaunchKernelEx(&cfg, k_anyprec_pipe<FP16>, g, d, f, geo);
+    return cudaLaunchKernelEx(&cfg, k_anyprec_pipe<BF16>, g, d, f, geo);
 }
 
 cudaError_t launch_ap_dequant(int dt, const uint32_t* qweight, const void* lut, void* out, uint32_t N, uint32_t K,

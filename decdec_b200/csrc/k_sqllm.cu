@@ -5,7 +5,7 @@
 namespace dd {
 
 template <int DT>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 3)
 k_sqllm(const __grid_constant__ SqParams g, const __grid_constant__ DecParams d, const __grid_constant__ FinParams f) {
     extern __shared__ __align__(128) unsigned char sm[];
     if (blockIdx.x < d.n_cta) dec_role<DT>(d, f, blockIdx.x, sm);

@@ -38,7 +38,7 @@ MODELS = {
 }
 BITS, GROUP = 3, 128
 # (n_tb, k_chunk of wqkv, wo, w1w3, w2) chosen by `python -m decdec_b200.tuner` for a 5 % layer slowdown budget
-# on one B200 (profiles/tuner_llama3-8b_lutgemm3.md); timed as an extra operating point beside k_chunk = 32
+# on one B200 (profiles/tuner_llama3-8b.md); timed as an extra operating point beside k_chunk = 32
 TUNED_5PCT = {"llama3-8b": "16:0,0,5,3"}
 NCU_TRAFFIC_RATIO = 51.72 / 51.53   # measured DRAM bytes / algorithmic bytes of k_bcq_pipe, profiles/k_bcq_pipe_*.md
 

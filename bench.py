@@ -181,7 +181,8 @@ def workload_config(args):
     return {"workload": f"{args.model} decode hot path: {layers} layers x (wqkv, wo, w1w3, w2) fused GEMV+DEC, "
                         f"{BITS}-bit binary-coded group-{GROUP} weights, 4-bit residual rows in pinned host memory",
             "k_chunk": args.k_chunk, "n_tb": args.n_tb, "batch": 1,
-            "parallelism": f"tp{args.gpus}" if args.gpus > 1 else "single",
+            "parallelism": (f"tp{args.gpus}, row-parallel outputs summed by " + ("a one-shot push kernel over NVLink peer memory"
+                            if args.allreduce == "push" else "ncclAllReduce")) if args.gpus > 1 else "single",
             "cache": "inputs larger than L2 (every layer has its own weights and residual; no L2 flush needed)"}
 
 
@@ -339,6 +340,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="use fewer layers (profiling captures only)")
     ap.add_argument("--tuned", default=None, help="extra operating point 'n_tb:k_wqkv,k_wo,k_w1w3,k_w2' ('' = skip; default: the tuner's 5 %% result for the model, single GPU only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--allreduce", default="push", choices=["push", "nccl"],
+                    help="multi-GPU: exchange of the row-parallel outputs (push = one-shot kernel over NVLink peer memory)")
     ap.add_argument("--micro", default="", help="single entry point: lutgemm | dec_lutgemm | anyprec | dec_anyprec | sqllm | dec")
     ap.add_argument("--n", type=int, default=28672)
     ap.add_argument("--k", type=int, default=4096)
@@ -366,6 +369,13 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     tp = world
+    allreduce = None
+    if dist is not None:
+        if args.allreduce == "push":
+            from decdec_b200.tp import PushAllReduce
+            allreduce = PushAllReduce(max(MODELS[args.model][1], 1024))
+        else:
+            allreduce = dist.all_reduce
 
     model, ctx, _keep = build_model(args, torch, ext, dev, rank, tp)
     widths, in_sets = make_inputs(torch, model, dev)
@@ -383,8 +393,8 @@ def main():
                     ext.dec_lutgemm(p["cfg"], xbuf[p["k"]], p["y"], p["qw"], p["alpha"], p["qb"], BITS, GROUP)
                 else:
                     ext.lutgemm_gemv(xbuf[p["k"]], p["y"], p["qw"], p["alpha"], p["qb"], BITS, GROUP)
-                if p["par"] == "row" and dist is not None:
-                    dist.all_reduce(p["y"])
+                if p["par"] == "row" and allreduce is not None:
+                    allreduce(p["y"])
 
     def load_inputs(i):
         for k in widths:
@@ -521,6 +531,8 @@ def main():
         if cpu:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
+    if dist is not None and args.allreduce == "push":
+        allreduce.check()          # raises if any wait for a peer ever ran out
     if dist is not None:
         # graphs that captured NCCL work must go before the communicator; leave without running
         # interpreter-exit destructors, which can block on a communicator with captured collectives

@@ -21,7 +21,7 @@ CSRC = PKG / "csrc"
 LIB = PKG / "libdecdec_b200.so"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-CU_SOURCES = ["host.cu", "k_dec.cu", "k_bcq.cu", "k_anyprec.cu", "k_sqllm.cu", "noalloc.cu"]
+CU_SOURCES = ["host.cu", "k_dec.cu", "k_bcq.cu", "k_anyprec.cu", "k_sqllm.cu", "noalloc.cu", "tp_allreduce.cu"]
 
 
 def _run(cmd, log=None):

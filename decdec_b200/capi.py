@@ -58,6 +58,14 @@ SIGNATURES = {
     "decdec_lutgemm_gemv": (_i, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _i, _i, _i, _vp]),
     "decdec_sqllm_gemv": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _i, _i, _vp]),
     "decdec_lutgemm_gemv_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _i, _i, _i, _vp]),
+    "decdec_tp_layout": (_i, [_u32, _u32, C.POINTER(_up), C.POINTER(_up), C.POINTER(_up), C.POINTER(_up)]),
+    "decdec_tp_create": (_i, [_u32, _u32, _u32, C.POINTER(_up), _vp]),
+    "decdec_tp_local_ptr": (_i, [_up, C.POINTER(_vp)]),
+    "decdec_tp_connect_ipc": (_i, [_up, _vp]),
+    "decdec_tp_connect_ptrs": (_i, [_up, C.POINTER(_up)]),
+    "decdec_tp_allreduce": (_i, [_up, _vp, _u32, _i, _vp]),
+    "decdec_tp_status": (_i, [_up, C.POINTER(_u32), C.POINTER(_u32)]),
+    "decdec_tp_destroy": (_i, [_up]),
     "decdec_anyprec_dequant": (_i, [_vp, _vp, _vp, _u32, _u32, _i, _i, _vp]),
     "decdec_dec_anyprec": (_i, [_up, _vp, _vp, _vp, _u32, _vp, _u32, _u32, _i, _i, _vp]),
     "decdec_dec_lutgemm": (_i, [_up, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _i, _i, _i, _vp]),

@@ -13,7 +13,9 @@ per-layer tensors are cut so that the same kernels run unchanged on every rank:
       so a shard keeps the global bucket bounds by carrying those two values at [0] and [k_local-1].
       Partial outputs are summed with one all-reduce of [N] values.
 
-All functions are pure tensor slicing (torch, CPU or GPU); the collective is the caller's.
+The sharding functions are pure tensor slicing (torch, CPU or GPU).  `PushAllReduce` is the collective for
+the row-parallel outputs on GPUs of one node: a one-shot push over NVLink peer memory (CUDA kernel behind
+`decdec_tp_allreduce`), set up through any `torch.distributed` process group.
 """
 from __future__ import annotations
 
@@ -112,3 +114,60 @@ def shard_input(x: torch.Tensor, mode: str, rank: int, world: int, group: int = 
     K = x.shape[-1]
     k0, k1 = k_ranges(K, world, group)[rank]
     return x[..., k0:k1].contiguous()
+
+
+class PushAllReduce:
+    """In-place sum of a [.., n] fp16/bf16/fp32 CUDA tensor over the ranks of `group`, one kernel per rank.
+
+    Every rank allocates an exchange buffer in the CUDA library, the 64-byte IPC handles travel once through
+    the process group, and each call pushes this rank's vector into the peers' buffers, waits (bounded) for
+    theirs and sums in rank order - identical results on all ranks, capturable in CUDA graphs.  All ranks must
+    make the same sequence of calls.  `check()` raises if a wait ever ran out (a peer did not arrive).
+    """
+
+    _DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+    def __init__(self, max_n: int, group=None, device=None):
+        import ctypes as C
+        import torch.distributed as dist
+        from . import capi
+        self._capi, self._C = capi, C
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        handle = (C.c_ubyte * 64)()
+        comm = C.c_size_t(0)
+        with torch.cuda.device(self.device):
+            capi.call("decdec_tp_create", self.world, self.rank, int(max_n), C.byref(comm), C.cast(handle, C.c_void_p))
+        self._comm = comm.value
+        mine = torch.tensor(list(bytes(handle)), dtype=torch.uint8, device=self.device)
+        gathered = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(gathered, mine, group=group)
+        blob = bytes(torch.stack(gathered).cpu().flatten().tolist())
+        if self.world > 1:
+            buf = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
+            with torch.cuda.device(self.device):
+                capi.call("decdec_tp_connect_ipc", self._comm, C.cast(buf, C.c_void_p))
+        dist.barrier(group=group)          # every buffer is zeroed and mapped before the first push
+
+    def __call__(self, y: torch.Tensor) -> torch.Tensor:
+        if not y.is_cuda or not y.is_contiguous():
+            raise ValueError("PushAllReduce needs a contiguous CUDA tensor")
+        stream = torch.cuda.current_stream(y.device).cuda_stream
+        self._capi.call("decdec_tp_allreduce", self._comm, y.data_ptr(), y.numel(), self._DT[y.dtype], stream)
+        return y
+
+    def status(self):
+        calls, err = self._C.c_uint32(0), self._C.c_uint32(0)
+        self._capi.call("decdec_tp_status", self._comm, self._C.byref(calls), self._C.byref(err))
+        return int(calls.value), int(err.value)
+
+    def check(self) -> None:
+        calls, err = self.status()
+        if err:
+            raise RuntimeError(f"PushAllReduce: a wait for a peer ran out (after {calls} completed calls); outputs were left unsummed")
+
+    def close(self) -> None:
+        if self._comm:
+            self._capi.call("decdec_tp_destroy", self._comm)
+            self._comm = 0

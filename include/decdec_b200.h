@@ -113,6 +113,31 @@ int decdec_lutgemm_gemv_noalloc(const void* x_dev, void* y_dev, const int32_t* q
                                 const void* q_bias, uint32_t N, uint32_t K, int bitwidth, int group_size, int dtype,
                                 void* stream);
 
+/* ---- tensor-parallel output exchange.  NO COUNTERPART IN THE REFERENCE (it has no tensor parallelism). -------
+ * One-shot push all-reduce of the [n] partial outputs of a row-parallel projection over NVLink peer memory:
+ * every rank stores its vector into every peer's buffer, raises a flag, waits (bounded) for the peers'
+ * flags and sums in rank order, in one kernel per rank.  Replaces ncclAllReduce for these 8-16 KB vectors.
+ *
+ *   decdec_tp_create       allocates this rank's exchange buffer on the current device; ipc_handle_out (64 bytes,
+ *                          may be null) receives its cudaIpcMemHandle_t for the other processes.
+ *   decdec_tp_connect_ipc  handles = [world][64] bytes, entry `rank` ignored: opens the peers' buffers.
+ *   decdec_tp_connect_ptrs same, for buffers that are already addressable (several GPUs in one process).
+ *   decdec_tp_allreduce    y_dev[n] <- sum over ranks, in place, on `stream`.  All ranks must make the same
+ *                          sequence of calls with the same n.  Capturable in a CUDA graph.  n <= max_n,
+ *                          n*sizeof(dtype) a multiple of 16, y_dev 16-byte aligned.
+ *   decdec_tp_status       calls completed and the error word (1 = a wait ran out: a peer did not arrive
+ *                          within DECDEC_TP_WAIT_POLLS polls, default 2^21, about a second; y was left unsummed).
+ *   decdec_tp_layout       byte offsets inside an exchange buffer (flags [world][64] u32, slots [2][world][stride]).
+ */
+int decdec_tp_layout(uint32_t world, uint32_t max_n, size_t* flags_off, size_t* slots_off, size_t* slot_stride, size_t* bytes);
+int decdec_tp_create(uint32_t world, uint32_t rank, uint32_t max_n, uintptr_t* comm_out, unsigned char* ipc_handle_out);
+int decdec_tp_local_ptr(uintptr_t comm, void** ptr_out);
+int decdec_tp_connect_ipc(uintptr_t comm, const unsigned char* handles);
+int decdec_tp_connect_ptrs(uintptr_t comm, const uintptr_t* peer_ptrs);
+int decdec_tp_allreduce(uintptr_t comm, void* y_dev, uint32_t n, int dtype, void* stream);
+int decdec_tp_status(uintptr_t comm, uint32_t* calls_out, uint32_t* error_out);
+int decdec_tp_destroy(uintptr_t comm);
+
 /* anyprec_dequant (reference: decdec.cu:386-393): out_dev dtype [N, K] dense weights. */
 int decdec_anyprec_dequant(const int32_t* qweight, const void* lut, void* out_dev,
                            uint32_t N, uint32_t K, int bitwidth, int dtype, void* stream);

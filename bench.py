@@ -340,7 +340,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="use fewer layers (profiling captures only)")
     ap.add_argument("--tuned", default=None, help="extra operating point 'n_tb:k_wqkv,k_wo,k_w1w3,k_w2' ('' = skip; default: the tuner's 5 %% result for the model, single GPU only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--allreduce", default="push", choices=["push", "nccl"],
+    ap.add_argument("--allreduce", default="nccl", choices=["push", "nccl"],
                     help="multi-GPU: exchange of the row-parallel outputs (push = one-shot kernel over NVLink peer memory)")
     ap.add_argument("--micro", default="", help="single entry point: lutgemm | dec_lutgemm | anyprec | dec_anyprec | sqllm | dec")
     ap.add_argument("--n", type=int, default=28672)

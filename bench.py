@@ -40,7 +40,7 @@ BITS, GROUP = 3, 128
 # (n_tb, k_chunk of wqkv, wo, w1w3, w2) chosen by `python -m decdec_b200.tuner` for a 5 % layer slowdown budget
 # on one B200 (profiles/tuner_llama3-8b.md); timed as an extra operating point beside k_chunk = 32
 TUNED_5PCT = {"llama3-8b": "16:0,0,5,3"}
-NCU_TRAFFIC_RATIO = 51.72 / 51.53   # measured DRAM bytes / algorithmic bytes of k_bcq_pipe, profiles/k_bcq_pipe_*.md
+NCU_TRAFFIC_RATIO = 51.73 / 51.50   # measured DRAM bytes / algorithmic bytes of k_bcq_pipe, profiles/k_bcq_pipe_*.md
 
 
 def projections(model: str, tp: int = 1, rank: int = 0):
@@ -511,7 +511,7 @@ def main():
             "decdec_off": {"value": 1e3 / ms_off, "unit": "tokens/s", "ms_per_step": ms_off,
                            "slowdown_on_vs_off": ms_on / ms_off},
             "roofline": {"bound": "hbm", "achieved": gemv_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gemv_gbs / hbm_peak,
-                         # ncu capture of the w1w3 launch (profiles/): dram read+write 51.72 MB for 51.53 MB algorithmic
+                         # ncu capture of the w1w3 launch (profiles/): dram read+write 51.73 MB for 51.50 MB algorithmic
                          "traffic": NCU_TRAFFIC_RATIO * hbm_bytes / calls, "kernel": "k_bcq_pipe<fp16,3> (GEMV role, compensation off)", "launches_per_step": calls,
                          "algorithmic_bytes_per_step": hbm_bytes, "peak_source": peak_src,
                          "note": "bytes of all GEMV launches of a step / event-timed duration of the step with compensation off"},

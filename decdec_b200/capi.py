@@ -58,6 +58,7 @@ SIGNATURES = {
     "decdec_lutgemm_gemv": (_i, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _i, _i, _i, _vp]),
     "decdec_sqllm_gemv": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _i, _i, _vp]),
     "decdec_lutgemm_gemv_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _i, _i, _i, _vp]),
+    "decdec_lutgemm_dequant": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _i, _i, _i, _vp]),
     "decdec_tp_layout": (_i, [_u32, _u32, C.POINTER(_up), C.POINTER(_up), C.POINTER(_up), C.POINTER(_up)]),
     "decdec_tp_create": (_i, [_u32, _u32, _u32, C.POINTER(_up), _vp]),
     "decdec_tp_local_ptr": (_i, [_up, C.POINTER(_vp)]),

@@ -316,7 +316,7 @@ __device__ void dec_fetch_direct(const DecParams& p, float* acc_g, uint32_t nrow
     const float* sact = reinterpret_cast<const float*>(sm + DecSmem::kAct);
     const uint32_t wpr = p.N / 8;
     const uint32_t nvec = (w1 - w0) / 4u;
-    uint32_t R = nthr / nvec;                       // row groups side by side (1..16 by the caller's choice of form)
+    uint32_t R = nthr / nvec;                       // row groups side by side (1..32 by the caller's choice of form)
     if (R == 0) R = 1;
     // R == 1: threads stride over the column vectors; R > 1: one sweep, thread -> (vector, row group)
     const uint32_t stride = R > 1 ? nvec * R : nthr;
@@ -377,8 +377,9 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
     const uint32_t w0 = min(wpr, t0 * f.tile_units * 4u);
     const uint32_t w1 = min(wpr, t1 * f.tile_units * 4u);
     const bool vec = (p.N % 32u) == 0u;
-    // wide column range: at most sixteen thread groups share a column vector
-    const bool direct = vec && (w1 - w0) * 4u >= nthr;
+    // wide column range: at most sixteen thread groups share a column vector - or up to thirty-two when so few
+    // rows are selected per chunk that every group gets one row and one load (small k_chunk on the narrow layers)
+    const bool direct = vec && ((w1 - w0) * 4u >= nthr || ((w1 - w0) * 8u >= nthr && p.k_chunk <= 16u));
     int* srow = reinterpret_cast<int*>(sm + DecSmem::kRow);
     float* sact = reinterpret_cast<float*>(sm + DecSmem::kAct);
     DD_STAMP(cta, 0);

@@ -201,4 +201,49 @@ __device__ void bcq_role(const BcqParams& p, const FinParams& f, uint32_t cta, u
     arrive_and_finalize<DT>(f, tile, tile + 1, s_flag);
 }
 
+// ---- dequantizer: binary-coded planes -> dense [K, N] (the operand of the prefill GEMM) -----------------
+// W[k][n] = DT( DT( sum_p (2*bit_p(k,n) - 1) * alpha[g][p][n] ) + q_bias[g][n] ): the same two roundings as the
+// reference's tensor expression (end-to-end/LUTGEMMLinear.py:41-82: plane sum in the layer dtype, then + q_bias).
+// Thread = (word row kw, output pair): reads the planes' words of two neighbouring outputs, writes 32 rows of
+// 2 x DT (4 or 8 bytes), so a warp writes 128-256 contiguous bytes per row.  Needs N % 2 == 0.
+template <int DT>
+__global__ void __launch_bounds__(kThreads) bcq_dequant_kernel(const uint32_t* __restrict__ qweight, const void* __restrict__ alpha_,
+                                                              const void* __restrict__ qbias_, void* __restrict__ out_, uint32_t N,
+                                                              uint32_t K, uint32_t bits, uint32_t group) {
+    using T = typename Tr<DT>::T;
+    const T* alpha = reinterpret_cast<const T*>(alpha_);
+    const T* qbias = reinterpret_cast<const T*>(qbias_);
+    T* out = reinterpret_cast<T*>(out_);
+    const uint32_t npair = N / 2;
+    const size_t total = (size_t)(K / 32) * npair;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t kw = (uint32_t)(idx / npair), n = 2u * (uint32_t)(idx % npair);
+        const uint32_t g = (kw * 32u) / group;
+        uint2 w[8];
+        float a0[8], a1[8];
+        for (uint32_t pl = 0; pl < bits; ++pl) {
+            w[pl] = *reinterpret_cast<const uint2*>(qweight + ((size_t)kw * bits + pl) * N + n);
+            a0[pl] = Tr<DT>::to_f(alpha[((size_t)g * bits + pl) * N + n]);
+            a1[pl] = Tr<DT>::to_f(alpha[((size_t)g * bits + pl) * N + n + 1]);
+        }
+        const T b0 = qbias[(size_t)g * N + n], b1 = qbias[(size_t)g * N + n + 1];
+        for (uint32_t j = 0; j < 32; ++j) {
+            float s0 = 0.0f, s1 = 0.0f;
+            for (uint32_t pl = 0; pl < bits; ++pl) {
+                s0 += ((w[pl].x >> j) & 1u) ? a0[pl] : -a0[pl];
+                s1 += ((w[pl].y >> j) & 1u) ? a1[pl] : -a1[pl];
+            }
+            T o[2];
+            if constexpr (DT == FP32) {
+                o[0] = s0 + b0; o[1] = s1 + b1;
+            } else {
+                o[0] = Tr<DT>::add(Tr<DT>::from_f(s0), b0);
+                o[1] = Tr<DT>::add(Tr<DT>::from_f(s1), b1);
+            }
+            T* dst = out + (size_t)(kw * 32u + j) * N + n;
+            dst[0] = o[0]; dst[1] = o[1];
+        }
+    }
+}
+
 }  // namespace dd

@@ -569,6 +569,21 @@ int decdec_anyprec_dequant(const int32_t* qw, const void* lut, void* out, uint32
     return 0;
 }
 
+int decdec_lutgemm_dequant(const int32_t* qw, const void* alpha, const void* q_bias, void* out, uint32_t N, uint32_t K, int bits,
+                           int group, int dtype, void* stream) {
+    if (!qw || !alpha || !q_bias || !out) return fail(DECDEC_E_INVALID, "null pointer argument");
+    if (!valid_dtype(dtype)) return fail(DECDEC_E_INVALID, "Unsupported data type.");
+    if (bits < 1 || bits > 8) return fail(DECDEC_E_INVALID, "Bitwidth must be between 1 and 8.");
+    if (N == 0 || K == 0) return fail(DECDEC_E_INVALID, "empty layer (N=%u, K=%u)", N, K);
+    if (K % 32u) return fail(DECDEC_E_INVALID, "in_features must be a multiple of 32, got %u", K);
+    if (group <= 0 || group % 32 || K % (uint32_t)group) return fail(DECDEC_E_INVALID, "group_size must be a multiple of 32 that divides in_features (got %d)", group);
+    if (N % 2u) return fail(DECDEC_E_UNSUPPORTED, "lutgemm dequant: out_features must be even, got %u", N);
+    if (reinterpret_cast<uintptr_t>(qw) & 7u) return fail(DECDEC_E_INVALID, "lutgemm dequant: q_weight must be 8-byte aligned");
+    DD_CUDA(launch_bcq_dequant(dtype, reinterpret_cast<const uint32_t*>(qw), alpha, q_bias, out, N, K, (uint32_t)bits,
+                               (uint32_t)group, reinterpret_cast<cudaStream_t>(stream)));
+    return 0;
+}
+
 int decdec_dec_anyprec(uintptr_t cfg, const void* x, void* y, const int32_t* qw, uint32_t planes, const void* lut,
                        uint32_t N, uint32_t K, int bits, int dtype, void* stream) {
     Config* c = reinterpret_cast<Config*>(cfg);

@@ -21,6 +21,8 @@ cudaError_t launch_anyprec_pipe(int dt, const ApParams& g, const DecParams& d, c
 cudaError_t launch_sqllm(int dt, const SqParams& g, const DecParams& d, const FinParams& f, cudaStream_t s);
 cudaError_t launch_ap_dequant(int dt, const uint32_t* qweight, const void* lut, void* out, uint32_t N, uint32_t K,
                               uint32_t bits, cudaStream_t s);
+cudaError_t launch_bcq_dequant(int dt, const uint32_t* qweight, const void* alpha, const void* q_bias, void* out, uint32_t N,
+                               uint32_t K, uint32_t bits, uint32_t group, cudaStream_t s);
 cudaError_t launch_burner(int blocks, long long iters, cudaStream_t s);
 
 int set_last_error(int code, const char* msg);

@@ -167,6 +167,20 @@ cudaError_t launch_bcq(int dt, const BcqParams& g, const DecParams& d, const Fin
     }
 }
 
+cudaError_t launch_bcq_dequant(int dt, const uint32_t* qweight, const void* alpha, const void* q_bias, void* out, uint32_t N,
+                               uint32_t K, uint32_t bits, uint32_t group, cudaStream_t s) {
+    const size_t total = (size_t)(K / 32) * (N / 2);
+    const size_t want = (total + kThreads - 1) / kThreads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (blocks == 0) return cudaSuccess;
+    switch (dt) {
+        case FP32: bcq_dequant_kernel<FP32><<<blocks, kThreads, 0, s>>>(qweight, alpha, q_bias, out, N, K, bits, group); break;
+        case FP16: bcq_dequant_kernel<FP16><<<blocks, kThreads, 0, s>>>(qweight, alpha, q_bias, out, N, K, bits, group); break;
+        default: bcq_dequant_kernel<BF16><<<blocks, kThreads, 0, s>>>(qweight, alpha, q_bias, out, N, K, bits, group); break;
+    }
+    return cudaGetLastError();
+}
+
 }  // namespace dd
 #ifdef DD_PROF
 extern "C" int decdec_debug_prof_bcq(unsigned long long* out, int n) {

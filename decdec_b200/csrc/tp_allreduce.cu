@@ -76,6 +76,8 @@ __global__ void __launch_bounds__(kTpThreads) k_tp_allreduce(const __grid_consta
     using T = typename Tr<DT>::T;
     constexpr uint32_t EPT = 16 / sizeof(T);                       // elements per 16-byte vector
     __shared__ uint32_t s_epoch, s_bad;
+    pdl_trigger();                 // the next kernel of the stream may become resident while this one exchanges
+    pdl_wait();                    // y comes from the previous kernel
     unsigned char* mine = a.peers[a.rank];
     uint32_t* hdr = reinterpret_cast<uint32_t*>(mine);
     if (threadIdx.x == 0) {
@@ -258,12 +260,23 @@ int decdec_tp_allreduce(uintptr_t comm, void* y_dev, uint32_t n, int dtype, void
     const uint32_t grid = (n + kTpThreads * ept - 1) / (kTpThreads * ept);
     if (grid > kTpMaxCta) return tp_fail(DECDEC_E_UNSUPPORTED, "tp: vector too long for the flag table");
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    // programmatic dependent launch: the blocks become resident while the GEMV before them drains
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kTpThreads);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    const char* pe = getenv("DECDEC_PDL");
+    attr[0].val.programmaticStreamSerializationAllowed = (pe && *pe == '0') ? 0 : 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e;
     switch (dtype) {
-        case FP32: k_tp_allreduce<FP32><<<grid, kTpThreads, 0, s>>>(a, y_dev); break;
-        case FP16: k_tp_allreduce<FP16><<<grid, kTpThreads, 0, s>>>(a, y_dev); break;
-        default: k_tp_allreduce<BF16><<<grid, kTpThreads, 0, s>>>(a, y_dev); break;
+        case FP32: e = cudaLaunchKernelEx(&cfg, k_tp_allreduce<FP32>, a, y_dev); break;
+        case FP16: e = cudaLaunchKernelEx(&cfg, k_tp_allreduce<FP16>, a, y_dev); break;
+        default: e = cudaLaunchKernelEx(&cfg, k_tp_allreduce<BF16>, a, y_dev); break;
     }
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return tp_fail(DECDEC_E_CUDA, "tp: launch failed: %s", cudaGetErrorString(e));
     return 0;
 }

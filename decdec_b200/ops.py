@@ -181,6 +181,23 @@ def anyprec_dequant(qweight, lut, bitwidth: int) -> torch.Tensor:
     return out
 
 
+def lutgemm_dequant(q_weight, alpha, q_bias, bitwidth: int, group_size: int) -> torch.Tensor:
+    """Dense [K, N] weights of a binary-coded layer (the right operand of the prefill `x @ W`); same arithmetic as the
+    reference's tensor expression, end-to-end/LUTGEMMLinear.py:41-82.  No counterpart in the reference binding."""
+    _check(q_weight.dim() == 3 and q_weight.dtype == torch.int32 and q_weight.is_cuda and alpha.is_cuda and q_bias.is_cuda,
+           "q_weight must be a 3-D int tensor on GPU")
+    _check(alpha.dtype == q_bias.dtype, "Mismatched data types between alpha and q_bias tensors.")
+    _check(q_weight.is_contiguous() and alpha.is_contiguous() and q_bias.is_contiguous(), "tensors must be contiguous.")
+    k, n = q_weight.size(0) * 32, q_weight.size(2)
+    _check(q_weight.size(1) == bitwidth and tuple(alpha.shape) == (k // group_size, bitwidth, n)
+           and tuple(q_bias.shape) == (k // group_size, n), "q_weight/alpha/q_bias shapes do not match bitwidth and group_size.")
+    out = torch.empty((k, n), dtype=alpha.dtype, device=q_weight.device)
+    with torch.cuda.device(q_weight.device):
+        _call("decdec_lutgemm_dequant", q_weight.data_ptr(), alpha.data_ptr(), q_bias.data_ptr(), out.data_ptr(), n, k,
+              int(bitwidth), int(group_size), _dt(alpha), _stream())
+    return out
+
+
 def _lutgemm_checks(input, output, q_weight, alpha, q_bias, bitwidth, group_size):
     _check(1 <= bitwidth <= 8, "Bitwidth must be between 1 and 8.")
     _check(input.dtype == alpha.dtype and input.dtype == q_bias.dtype and input.dtype == output.dtype,

@@ -113,6 +113,13 @@ int decdec_lutgemm_gemv_noalloc(const void* x_dev, void* y_dev, const int32_t* q
                                 const void* q_bias, uint32_t N, uint32_t K, int bitwidth, int group_size, int dtype,
                                 void* stream);
 
+/* Dense weights of a binary-coded layer for the prefill GEMM.  NO COUNTERPART IN THE REFERENCE BINDING: the reference
+ * builds this tensor with a chain of torch ops on every prefill call (end-to-end/LUTGEMMLinear.py:41-82).
+ * out_dev dtype [K, N] (in_features x out_features, the right operand of `x @ W`), same arithmetic as that
+ * expression: the planes' +-alpha are summed, rounded to dtype, and q_bias is added in dtype. */
+int decdec_lutgemm_dequant(const int32_t* qweight, const void* alpha, const void* q_bias, void* out_dev,
+                           uint32_t N, uint32_t K, int bitwidth, int group_size, int dtype, void* stream);
+
 /* ---- tensor-parallel output exchange.  NO COUNTERPART IN THE REFERENCE (it has no tensor parallelism). -------
  * One-shot push all-reduce of the [n] partial outputs of a row-parallel projection over NVLink peer memory:
  * every rank stores its vector into every peer's buffer, raises a flag, waits (bounded) for the peers'

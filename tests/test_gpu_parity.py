@@ -5,6 +5,8 @@ Tolerances (north star): fp16 outputs max abs err <= 1e-2 and rel L2 <= 1e-3 aga
 oracle; bf16 outputs carry 8 mantissa bits, so 8e-2 / 6e-3; fp32 1e-3 / 1e-5.  Channel selection is
 compared bit-exactly (rows and recorded activations).
 """
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -90,6 +92,42 @@ def test_lutgemm_down_proj_fp16(ops):
     y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
     ops.lutgemm_gemv(x.cuda(), y, L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda(), 3, 128)
     _assert_close(y, ofw.layer_output(L["w_hat"], P.to_np(x)), "fp16", "lutgemm down")
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16", "fp32"])
+@pytest.mark.parametrize("N,K,bits,group", [(4096, 1024, 3, 128), (48, 256, 3, 128), (130, 96, 4, 32), (256, 512, 1, 64), (64, 2048, 8, 256)])
+def test_lutgemm_dequant_prefill_operand(ops, dtype, N, K, bits, group):
+    """Dense [K, N] operand of the prefill GEMM: bit-exact against the reference's arithmetic
+    (LUTGEMMLinear.py:41-82: plane sum rounded to the layer dtype, then + q_bias in that dtype)."""
+    L = P.random_bcq_layer(N, K, bits, group, seed=N + K + bits, dtype=dtype)
+    out = ops.lutgemm_dequant(L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda(), bits, group)
+    assert out.shape == (K, N) and out.dtype == P.TORCH_DT[dtype]
+    # emulation with the same roundings on the CPU (fp32 plane sum in plane order)
+    words = L["qweight"].numpy().view(np.uint32)                                        # [K/32, bits, N]
+    bit = ((words[:, None, :, :] >> np.arange(32, dtype=np.uint32)[None, :, None, None]) & 1).reshape(K, bits, N)
+    sign = torch.from_numpy(bit.astype(np.float32) * 2 - 1)
+    gidx = torch.arange(K) // group
+    a = L["alpha"].float()[gidx]                                                         # [K, bits, N]
+    s32 = torch.zeros(K, N)
+    for p in range(bits):
+        s32 = s32 + sign[:, p, :] * a[:, p, :]
+    exp = s32.to(P.TORCH_DT[dtype]) + L["q_bias"][gidx]
+    assert torch.equal(out.cpu(), exp), "dequantized operand differs from the two-rounding arithmetic"
+    # and it is the matrix the GEMV kernels use
+    rel = {"fp16": 2.0 ** -9, "bf16": 2.0 ** -6, "fp32": 1e-6}[dtype]          # two roundings to the layer dtype
+    assert np.abs(P.to_np(out).T - L["w_hat"]).max() <= rel * np.abs(L["w_hat"]).max() + 1e-7
+
+
+def test_lutgemm_dequant_matches_reference_output(ops):
+    """Against the reference's own `lutgemm_dequant` output on the committed fixture (tests/golden)."""
+    d = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "lutgemm_dequant.npz"))
+    out = ops.lutgemm_dequant(torch.from_numpy(d["binary"]).cuda(), torch.from_numpy(d["alpha"]).cuda(),
+                              torch.from_numpy(d["q_bias"]).cuda(), 3, int(d["group"]))
+    ref = d["dense"]
+    got = out.float().cpu().numpy()
+    if ref.shape != got.shape:
+        ref = ref.T
+    assert np.abs(got - ref).max() <= 2 * 2.0 ** -16          # the reference sums the planes in fp16: <= 2 half ulps at |w| ~ 0.03
 
 
 # ------------------------------------------------------------------------------------------------

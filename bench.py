@@ -379,6 +379,10 @@ def main():
 
     model, ctx, _keep = build_model(args, torch, ext, dev, rank, tp)
     widths, in_sets = make_inputs(torch, model, dev)
+    if dist is not None:
+        # ranks finish their set-up seconds apart; the push exchange waits for a peer for about a second only
+        dist.barrier()
+        torch.cuda.synchronize()
     xbuf = {k: torch.zeros(1, 1, k, dtype=torch.float16, device=dev) for k in widths}
     pinned_in = [{k: v.pin_memory() for k, v in s.items()} for s in in_sets]
     out_host = torch.zeros(1, 1, model[0][-1]["n"], dtype=torch.float16).pin_memory()

@@ -109,10 +109,14 @@ __global__ void __launch_bounds__(kTpThreads) k_tp_allreduce(const __grid_consta
         const uint32_t* flag = reinterpret_cast<const uint32_t*>(mine + a.flags_off) + threadIdx.x * kTpMaxCta + blockIdx.x;
         uint32_t polls = 0;
         // flags only grow; a peer that is one call ahead shows e + 1
-        while ((int32_t)(ld_acquire_sys(flag) - e) < 0) {
+        uint32_t seen;
+        while ((int32_t)((seen = ld_acquire_sys(flag)) - e) < 0) {
             if (++polls >= a.wait_polls) { atomicExch(&s_bad, 1u); break; }
             __nanosleep(64);
         }
+        // two or more calls ahead can only happen after this rank missed a bounded wait of the peer: the
+        // slot of this parity may already hold a later vector, so the sum is not formed
+        if ((int32_t)(seen - e) >= 2) atomicExch(&s_bad, 1u);
     }
     __syncthreads();
 

@@ -122,7 +122,8 @@ class PushAllReduce:
     Every rank allocates an exchange buffer in the CUDA library, the 64-byte IPC handles travel once through
     the process group, and each call pushes this rank's vector into the peers' buffers, waits (bounded) for
     theirs and sums in rank order - identical results on all ranks, capturable in CUDA graphs.  All ranks must
-    make the same sequence of calls.  `check()` raises if a wait ever ran out (a peer did not arrive).
+    make the same sequence of calls, and no rank may reach a call more than the bounded wait (about a second) after
+    the others - put a barrier after uneven set-up work.  `check()` raises if a wait ever ran out.
     """
 
     _DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}

@@ -85,7 +85,7 @@ class ClockSampler:
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         self.p = None
         try:
-            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                                        "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             self.p = None
@@ -480,10 +480,10 @@ def main():
 
     sampler = ClockSampler(local) if rank == 0 else None
     ms_on = timed(True, args.steps, args.warmup, e2e=False)
-    clocks = sampler.stop() if sampler else {}
     ms_off = timed(False, args.steps, args.warmup, e2e=False)
     ms_e2e = timed(True, args.steps, args.warmup, e2e=True)
     ms_tuned = timed("tuned", args.steps, args.warmup, e2e=False) if "tuned" in graphs else None
+    clocks = sampler.stop() if sampler else {}      # sampled across all timed regions of the run
 
     n_layers = len(model)
     calls = n_layers * len(model[0])

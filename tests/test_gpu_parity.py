@@ -346,6 +346,30 @@ def test_dec_anyprec_config1_sweep(ops, k_chunk):
     _assert_close(y, ofw.layer_output(L["w_hat"], P.to_np(x), None, delta), "fp16", f"dec_anyprec kc={k_chunk}")
 
 
+@pytest.mark.parametrize("N,K,k_chunk,n_tb", [(14336, 4096, 64, 96), (14336, 4096, 8, 16), (4096, 14336, 16, 32), (4096, 4096, 32, 64)])
+def test_dec_anyprec_config1_full_shapes(ops, N, K, k_chunk, n_tb):
+    """BASELINE config 1 at the full Llama-3-8B projection sizes (gate/up, down, q/o), random 3-bit codes and LUTs."""
+    L = P.lut_layer(N, K, 3, seed=N + k_chunk, real=False)
+    cs, rs = P.random_residual(N, K, seed=45)
+    thr = P.make_thresholds(K)
+    x = P.make_activation(K, seed=43)
+    ctx, rows, acts = _ctx(ops, n_tb, 32 * 1024, "fp16")
+    cfg = ops.create_dec_config(ctx, k_chunk, cs, rs, thr)
+    y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+    ops.dec_anyprec(cfg, x.cuda(), y, L["qweight"].cuda(), L["lut"].cuda(), 3)
+    torch.cuda.synchronize()
+    exp_rows, exp_acts, _ = P.expected_selection(x, thr, k_chunk, "fp16")
+    k = k_chunk * K // 1024
+    assert np.array_equal(rows[:k].cpu().numpy(), exp_rows)
+    delta = ofw.dec_delta(P.to_np(x), exp_rows, cs.numpy(), P.to_np(rs), exp_acts)
+    ma, rl = P.errors(y, ofw.layer_output(L["w_hat"], P.to_np(x), None, delta))
+    # rel L2 as everywhere; the max-abs bound is 3e-2 here: the any-precision kernel adds 8 products in half2 before it
+    # goes to fp32 (the reference adds in half too), and with x20 outliers over up to 14336 channels single outputs of
+    # magnitude 10-30 land 1-2 fp16 ulps (0.008-0.016 each) from the float64 value
+    assert rl <= TOL["fp16"][1] and ma <= 3e-2, f"dec_anyprec {N}x{K} kc={k_chunk}: max abs {ma:.3e}, rel L2 {rl:.3e}"
+    ops.destroy_dec_config(cfg)
+
+
 @pytest.mark.parametrize("bits", [3, 4])
 def test_dec_sqllm(ops, bits):
     N, K = 512, 2048

@@ -412,6 +412,44 @@ def test_anyprec_gemv(ops, dtype, N, K, bits):
     _assert_close(y, ref, dtype, f"anyprec {N}x{K} b{bits} {dtype}")
 
 
+@pytest.mark.parametrize("entry", ["anyprec", "sqllm", "lutgemm", "dec_lutgemm"])
+def test_output_views_and_odd_widths(ops, entry):
+    """Outputs that are not 8-byte aligned (a view one element into a buffer) and widths that are not a multiple
+    of four take the scalar path of the finalizer; the elements around the view must stay untouched."""
+    K = 2048
+    N = {"anyprec": 131, "sqllm": 70, "lutgemm": 264, "dec_lutgemm": 264}[entry]
+    x = P.make_activation(K, seed=71)
+    big = torch.full((1, 1, N + 3), 7.0, dtype=torch.float16, device="cuda")
+    y = big[:, :, 1:1 + N]
+    assert y.data_ptr() % 8 != 0
+    y.zero_()
+    if entry == "anyprec":
+        L = P.lut_layer(N, K, 3, seed=72)
+        ops.anyprec_gemv(x.cuda(), y, L["qweight"].cuda(), L["lut"].cuda(), 3)
+        ref = ofw.layer_output(L["w_hat"], P.to_np(x))
+    elif entry == "sqllm":
+        L = P.lut_layer(N, K, 3, seed=73, fmt="sqllm")
+        ops.sqllm_gemv(x.cuda(), y, L["qweight"].cuda(), L["lut"].cuda(), 3)
+        ref = ofw.layer_output(L["w_hat"], P.to_np(x))
+    else:
+        L = P.bcq_layer(N, K, 3, 128, seed=74)
+        if entry == "lutgemm":
+            ops.lutgemm_gemv(x.cuda(), y, L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda(), 3, 128)
+            ref = ofw.layer_output(L["w_hat"], P.to_np(x))
+        else:
+            cs, rs = P.random_residual(N, K, seed=75)
+            thr = P.make_thresholds(K)
+            ctx, rows, acts = _ctx(ops, 8, 1024, "fp16")
+            cfg = ops.create_dec_config(ctx, 8, cs, rs, thr)
+            ops.dec_lutgemm(cfg, x.cuda(), y, L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda(), 3, 128)
+            exp_rows, exp_acts, _ = P.expected_selection(x, thr, 8, "fp16")
+            delta = ofw.dec_delta(P.to_np(x), exp_rows, cs.numpy(), P.to_np(rs), exp_acts)
+            ref = ofw.layer_output(L["w_hat"], P.to_np(x), None, delta)
+    torch.cuda.synchronize()
+    _assert_close(y, ref, "fp16", f"{entry} into an unaligned view")
+    assert float(big[0, 0, 0]) == 7.0 and float(big[0, 0, N + 1]) == 7.0 and float(big[0, 0, N + 2]) == 7.0
+
+
 @pytest.mark.parametrize("bits,K", [(3, 4096), (3, 1536), (4, 2048), (8, 1024), (3, 96)])
 def test_anyprec_dequant_exact_and_extra_planes(ops, bits, K):
     """Dequantized weights equal lut[code] exactly; a tensor with more planes than `bitwidth` is

@@ -160,12 +160,24 @@ int fill_dec(const Config* c, const void* x, bool fused_select, uint32_t n_tiles
 // SMs left to the GEMV thread blocks of a fused launch.  A few compensation thread blocks take their SMs
 // out of the GEMV's single wave (the GEMV grid shrinks accordingly); many of them mean the launch is bound
 // by the host link anyway, and the GEMV keeps its full grid and runs in the gaps.
+uint32_t device_sms() {
+    static uint32_t sms[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!sms[dev]) {
+        int n = 0;
+        sms[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? (uint32_t)n : 148u;
+    }
+    return sms[dev];
+}
+
 uint32_t gemv_sm_budget(const Config* c, bool fused_select) {
-    if (!c) return 148;
+    const uint32_t sms = device_sms();
+    if (!c) return sms;
     DecParams d;
     memset(&d, 0, sizeof(d));
     dec_geometry(c, fused_select, 1u << 20, &d);
-    return d.n_cta <= 40 ? 148 - d.n_cta : 148;
+    return d.n_cta <= sms / 4 + 3 ? sms - d.n_cta : sms;      // up to 40 compensation blocks on a 148-SM part
 }
 
 int check_cfg_call(const Config* c, const void* x, void* y, uint32_t K, uint32_t N, int dtype) {

@@ -1,7 +1,7 @@
 """Generates the golden vectors under tests/golden/ by running the REFERENCE's own Python functions
-(SNU-ARC/DecDEC checked out at REF, default /root/reference) on small seeded inputs.
+(SNU-ARC/DecDEC checked out at REF, the first argument) on small seeded inputs.
 
-    python tests/golden/make_golden.py [REF]
+    python tests/golden/make_golden.py REF
 
 Functions exercised (CPU torch, no GPU needed):
   decdec_setup/cheatsheet.py:_process_layer                      residual quantizer + packer
@@ -19,7 +19,9 @@ import types
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: python " + sys.argv[0] + " <path of the SNU-ARC/DecDEC checkout>")
+REF = sys.argv[1]
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 

@@ -1,8 +1,8 @@
 """Generates tests/golden/tuner_cases.json by running the REFERENCE's search function
-(autotuner/tuner.py:tuner of SNU-ARC/DecDEC checked out at REF, default /root/reference) on seeded synthetic
+(autotuner/tuner.py:tuner of SNU-ARC/DecDEC checked out at REF, the first argument) on seeded synthetic
 timing tables.
 
-    python tests/golden/make_tuner_golden.py [REF]
+    python tests/golden/make_tuner_golden.py REF
 
 `tuner.py` imports matplotlib and its Nsight parser at module level; neither is used by the search, so both
 are replaced by empty stand-in modules for the import.  The tables are synthetic cost models (a launch floor,
@@ -19,7 +19,9 @@ import types
 
 import numpy as np
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: python " + sys.argv[0] + " <path of the SNU-ARC/DecDEC checkout>")
+REF = sys.argv[1]
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 DIMS = {"qkv": (4096, 6144), "o": (4096, 4096), "gu": (4096, 28672), "d": (14336, 4096)}

@@ -227,7 +227,7 @@ def build_model(args, torch, ext, dev, rank, tp):
         for p in layer:
             p["y"] = ybuf[off:off + p["n"]].view(1, 1, p["n"])
             off += p["n"]
-    return model, ctx, (rows, acts, ybuf)
+    return model, ctx, (rows, acts, ybuf, host_res)
 
 
 def make_inputs(torch, model, dev, n_sets=4):
@@ -340,6 +340,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="use fewer layers (profiling captures only)")
     ap.add_argument("--tuned", default=None, help="extra operating point 'n_tb:k_wqkv,k_wo,k_w1w3,k_w2' ('' = skip; default: the tuner's 5 %% result for the model, single GPU only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--resident-n-tb", type=int, default=32, help="thread-block budget of the residual-in-HBM operating point")
+    ap.add_argument("--no-resident", action="store_true",
+                    help="skip the extra operating point with the residual held in HBM instead of pinned host memory")
     ap.add_argument("--allreduce", default="nccl", choices=["push", "nccl"],
                     help="multi-GPU: exchange of the row-parallel outputs (push = one-shot kernel over NVLink peer memory)")
     ap.add_argument("--micro", default="", help="single entry point: lutgemm | dec_lutgemm | anyprec | dec_anyprec | sqllm | dec")
@@ -435,6 +438,30 @@ def main():
             with torch.cuda.graph(g, stream=stream):
                 token(True)
             graphs["tuned"] = g
+        # extra operating point: the same compensation with the residual resident in HBM (3.5 GB for this model, which a
+        # 180 GB part can afford) - what is left of the cost once the host link is out of the picture
+        if world == 1 and not args.no_resident:
+            dev_cfgs = []
+            ctx_r = ext.create_dec_context(args.resident_n_tb, _keep[0], _keep[1])
+            for layer in model:
+                for p in layer:
+                    q, sc, thr = _keep[3][p["name"]]
+                    dev_cfgs.append(ext.create_dec_config(ctx_r, args.k_chunk, q.to(dev), sc, thr))
+
+            def token_resident():
+                _keep[2].zero_()
+                i = 0
+                for layer in model:
+                    for p in layer:
+                        ext.dec_lutgemm(dev_cfgs[i], xbuf[p["k"]], p["y"], p["qw"], p["alpha"], p["qb"], BITS, GROUP)
+                        i += 1
+
+            token_resident()
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                token_resident()
+            graphs["resident"] = g
     torch.cuda.synchronize()
 
     def barrier():
@@ -483,6 +510,7 @@ def main():
     ms_off = timed(False, args.steps, args.warmup, e2e=False)
     ms_e2e = timed(True, args.steps, args.warmup, e2e=True)
     ms_tuned = timed("tuned", args.steps, args.warmup, e2e=False) if "tuned" in graphs else None
+    ms_res = timed("resident", args.steps, args.warmup, e2e=False) if "resident" in graphs else None
     clocks = sampler.stop() if sampler else {}      # sampled across all timed regions of the run
 
     n_layers = len(model)
@@ -532,6 +560,10 @@ def main():
                              "slowdown_vs_off": ms_tuned / ms_off, "n_tb": tuned_cfg["n_tb"], "k_chunk": tuned_cfg["k_chunk"],
                              "fetched_bytes_per_step": tb,
                              "note": "operating point of the (n_tb, k_chunk) tuner for a 5 % layer slowdown budget"}
+        if ms_res is not None:
+            line["residual_in_hbm"] = {"value": 1e3 / ms_res, "unit": "tokens/s", "ms_per_step": ms_res, "slowdown_vs_off": ms_res / ms_off,
+                                       "k_chunk": args.k_chunk, "n_tb": args.resident_n_tb, "hbm_bytes_for_residual": int(link_bytes / args.k_chunk * 1024) if args.k_chunk else 0,
+                                       "note": "same launches with q_residual in device memory (create_dec_config accepts a CUDA tensor); not the reference's operating mode"}
         if cpu:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)

@@ -329,6 +329,28 @@ def test_compensation_geometry_sweep(ops, entry, n_tb, k_chunk):
     ops.destroy_dec_config(cfg)
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp32"])
+@pytest.mark.parametrize("n_tb,k_chunk", [(2, 9), (4, 3), (16, 2), (96, 32)])
+def test_compensation_geometry_other_dtypes(ops, dtype, n_tb, k_chunk):
+    """Direct and grouped fetch with bf16 / fp32 activations, scales and outputs (compensation alone)."""
+    N, K = 4096, 2048
+    cs, rs = P.random_residual(N, K, seed=81, dtype=dtype)
+    thr = P.make_thresholds(K, dtype)
+    x = P.make_activation(K, seed=82, dtype=dtype)
+    ctx, rows, acts = _ctx(ops, n_tb, 32 * 1024, dtype)
+    cfg = ops.create_dec_config(ctx, k_chunk, cs, rs, thr)
+    y0 = _y0(N, dtype)
+    y = y0.clone().cuda()
+    ops.dec(cfg, x.cuda(), y)
+    torch.cuda.synchronize()
+    exp_rows, exp_acts, _ = P.expected_selection(x, thr, k_chunk, dtype)
+    k = k_chunk * K // 1024
+    assert np.array_equal(rows[:k].cpu().numpy(), exp_rows)
+    delta = ofw.dec_delta(P.to_np(x), exp_rows, cs.numpy(), P.to_np(rs), exp_acts)
+    _assert_close(y, P.to_np(y0).reshape(-1) + delta, dtype, f"dec {dtype} n_tb={n_tb} k_chunk={k_chunk}")
+    ops.destroy_dec_config(cfg)
+
+
 @pytest.mark.parametrize("k_chunk", [0, 8, 16, 32, 64])
 def test_dec_anyprec_config1_sweep(ops, k_chunk):
     """BASELINE config 1 (k/v projection shape 4096 -> 1024), 3-bit LUT, k_chunk sweep."""

@@ -161,6 +161,11 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun sets OMP_NUM_THREADS=1 for its ranks; the CPU arm uses every core this process may run on
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
+    except (AttributeError, RuntimeError):
+        pass
     cores = torch.get_num_threads()
     ts, desc, scale = cpu_sample(args.model, args.k_chunk, args.steps, max(1, args.warmup))
     total = sum(ts)
@@ -532,6 +537,10 @@ def main():
     if rank == 0:
         cpu = None
         if not args.no_cpu_baseline:
+            try:
+                torch.set_num_threads(len(os.sched_getaffinity(0)))      # torchrun pins ranks to one OpenMP thread
+            except (AttributeError, RuntimeError):
+                pass
             ts, desc, scale = cpu_sample(args.model, args.k_chunk, 5, 1)
             cpu = {"value": len(ts) / (sum(ts) * scale), "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                    "sample": desc + f"; 5 repetitions, scaled x{scale:.0f} to a token"}

@@ -47,6 +47,27 @@ def test_status_codes_without_gpu(capi):
     assert e.value.code == -1 and "3 or 4" in str(e.value)
 
 
+def test_added_entry_points_without_gpu(capi):
+    """Host-side checks of the entry points that have no reference counterpart (no device work)."""
+    f, s, st, b = C.c_size_t(), C.c_size_t(), C.c_size_t(), C.c_size_t()
+    assert capi.lib.decdec_tp_layout(2, 4096, C.byref(f), C.byref(s), C.byref(st), C.byref(b)) == 0
+    assert f.value == 256 and s.value % 256 == 0 and s.value >= f.value + 2 * 64 * 4
+    assert st.value >= 4096 * 4 and st.value % 256 == 0
+    assert b.value == s.value + 2 * 2 * st.value                       # two halves x world slots
+    assert capi.lib.decdec_tp_layout(8, 8192, None, None, None, C.byref(b)) == 0 and b.value > 2 * 8 * 8192 * 4
+    assert capi.lib.decdec_tp_layout(9, 4096, None, None, None, None) == -1      # world out of range
+    assert capi.lib.decdec_tp_layout(0, 4096, None, None, None, None) == -1
+    h = C.c_size_t(0)
+    assert capi.lib.decdec_tp_create(2, 2, 4096, C.byref(h), None) == -1          # rank >= world
+    assert capi.lib.decdec_tp_create(2, 0, 0, C.byref(h), None) != 0              # empty vector
+    assert capi.lib.decdec_tp_allreduce(0, 16, 1024, capi.FP16, None) == -1       # null communicator
+    assert capi.lib.decdec_tp_destroy(0) == 0
+    assert capi.lib.decdec_lutgemm_dequant(16, 16, 16, 16, 64, 1024, 9, 128, capi.FP16, None) == -1
+    assert b"Bitwidth must be between 1 and 8" in capi.lib.decdec_last_error()
+    assert capi.lib.decdec_lutgemm_dequant(16, 16, 16, 16, 63, 1024, 3, 128, capi.FP16, None) != 0      # odd out_features
+    assert capi.lib.decdec_lutgemm_dequant(16, 16, 16, 16, 64, 1024, 3, 100, capi.FP16, None) == -1     # bad group
+
+
 def test_drop_in_module_surface():
     """`import decdec_ext` gives the 17 functions of the reference binding (bindings.cpp:19-40) and the
     tensor checks run before any device work."""

@@ -9,9 +9,12 @@
 //  * the bucket that overflows the quota gives its lowest channel indices (the reference takes
 //    whichever rows arrive first at a shared-memory atomic, dec.cu:146-154), and the published order
 //    is reproducible; ranks come from warp ballots and bit-matrix transposes, not atomics;
-//  * residual rows are fetched with 16-byte streaming loads, eight rows in flight per thread;
-//  * the dot products are accumulated in fp32 and scaled once per output; partial sums of the row
-//    groups of a CTA are combined through shared memory without atomics.
+//  * residual rows are fetched with 16-byte streaming loads, up to eight rows in flight per thread, in
+//    one of two forms chosen by the width of the CTA's column range: `dec_fetch_direct` (all threads of
+//    the CTA, sums added with 16-byte vector reductions, no barrier) and `dec_fetch` (256 threads, row
+//    groups combined through shared memory);
+//  * the dot products are accumulated in fp32 and go UNSCALED into their own accumulator; the output
+//    scale is applied once per output by the CTA that finalizes the tile (common.cuh).
 #pragma once
 #include "common.cuh"
 

@@ -554,9 +554,10 @@ def main():
             "roofline": {"bound": "hbm", "achieved": gemv_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gemv_gbs / hbm_peak,
                          # ncu capture of the w1w3 launch (profiles/): dram read+write 51.73 MB for 51.50 MB algorithmic
                          "traffic": NCU_TRAFFIC_RATIO * hbm_bytes / calls, "kernel": "k_bcq_pipe<fp16,3> (GEMV role, compensation off)", "launches_per_step": calls,
-                         "algorithmic_bytes_per_step": hbm_bytes, "peak_source": peak_src,
+                         "algorithmic_bytes_per_step": hbm_bytes, "peak_source": peak_src, "frac_of_spec_8000": gemv_gbs / 8000.0,
                          "note": "bytes of all GEMV launches of a step / event-timed duration of the step with compensation off"},
-            "host_link": {"achieved": link_gbs, "unit": "GB/s", "peak_spec": 64.0, "fetched_bytes_per_step": link_bytes,
+            "host_link": {"achieved": link_gbs, "unit": "GB/s", "peak_spec": 64.0, "frac_of_spec": link_gbs / 64.0,
+                          "measured_h2d_memcpy_peak": 55.4, "fetched_bytes_per_step": link_bytes,
                           "note": "residual bytes of a step / event-timed duration of the step with compensation on (lower bound of the link rate)"},
             "e2e": {"value": 1e3 / ms_e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e},

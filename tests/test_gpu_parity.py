@@ -351,6 +351,32 @@ def test_compensation_geometry_other_dtypes(ops, dtype, n_tb, k_chunk):
     ops.destroy_dec_config(cfg)
 
 
+def test_fused_projection_artifacts_feed_the_kernel(ops):
+    """q/k/v residuals fused by decdec_b200.artifacts (scales re-derived for the fused width) give the same
+    compensation as the three projections one after the other."""
+    from decdec_b200 import artifacts as A
+    K, widths = 2048, (1024, 256, 256)
+    parts, dense = [], []
+    for i, n in enumerate(widths):
+        cs, rs = P.random_residual(n, K, seed=90 + i)
+        parts.append({"cheatsheet": cs, "reordered_scales": rs})
+        dense.append(A.residual_matrix(cs, rs))
+    fused = A.fuse_projections(parts)
+    N = sum(widths)
+    thr = P.make_thresholds(K)
+    x = P.make_activation(K, seed=93)
+    ctx, rows, acts = _ctx(ops, 12, 32 * 1024, "fp16")
+    cfg = ops.create_dec_config(ctx, 16, fused["cheatsheet"], fused["reordered_scales"], thr)
+    y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+    ops.dec(cfg, x.cuda(), y)
+    torch.cuda.synchronize()
+    exp_rows, exp_acts, _ = P.expected_selection(x, thr, 16, "fp16")
+    R = torch.cat(dense, dim=0).double().numpy()                          # [N, K]
+    ref = R[:, exp_rows] @ exp_acts.astype(np.float64)
+    _assert_close(y, ref, "fp16", "dec with fused q/k/v artifacts")
+    ops.destroy_dec_config(cfg)
+
+
 @pytest.mark.parametrize("k_chunk", [0, 8, 16, 32, 64])
 def test_dec_anyprec_config1_sweep(ops, k_chunk):
     """BASELINE config 1 (k/v projection shape 4096 -> 1024), 3-bit LUT, k_chunk sweep."""

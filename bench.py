@@ -186,8 +186,8 @@ def workload_config(args):
     return {"workload": f"{args.model} decode hot path: {layers} layers x (wqkv, wo, w1w3, w2) fused GEMV+DEC, "
                         f"{BITS}-bit binary-coded group-{GROUP} weights, 4-bit residual rows in pinned host memory",
             "k_chunk": args.k_chunk, "n_tb": args.n_tb, "batch": 1,
-            "parallelism": (f"tp{args.gpus}, row-parallel outputs summed by " + ({"push": "a one-shot push kernel over NVLink peer memory", "fused": "a push over NVLink peer memory inside the GEMV finalizer",
-                             "nccl": "ncclAllReduce"}[args.allreduce])) if args.gpus > 1 else "single",
+            "parallelism": (f"tp{args.gpus}, row-parallel outputs summed by " + ("a one-shot push kernel over NVLink peer memory"
+                            if args.allreduce == "push" else "ncclAllReduce")) if args.gpus > 1 else "single",
             "cache": "inputs larger than L2 (every layer has its own weights and residual; no L2 flush needed)"}
 
 
@@ -348,8 +348,8 @@ def main():
     ap.add_argument("--resident-n-tb", type=int, default=32, help="thread-block budget of the residual-in-HBM operating point")
     ap.add_argument("--no-resident", action="store_true",
                     help="skip the extra operating point with the residual held in HBM instead of pinned host memory")
-    ap.add_argument("--allreduce", default="nccl", choices=["fused", "push", "nccl"],
-                    help="multi-GPU: exchange of the row-parallel outputs (push = one-shot kernel over NVLink peer memory; fused = the same push inside the GEMV's finalizer)")
+    ap.add_argument("--allreduce", default="nccl", choices=["push", "nccl"],
+                    help="multi-GPU: exchange of the row-parallel outputs (push = one-shot kernel over NVLink peer memory)")
     ap.add_argument("--micro", default="", help="single entry point: lutgemm | dec_lutgemm | anyprec | dec_anyprec | sqllm | dec")
     ap.add_argument("--n", type=int, default=28672)
     ap.add_argument("--k", type=int, default=4096)
@@ -379,7 +379,7 @@ def main():
     tp = world
     allreduce = None
     if dist is not None:
-        if args.allreduce in ("push", "fused"):
+        if args.allreduce == "push":
             from decdec_b200.tp import PushAllReduce
             allreduce = PushAllReduce(max(MODELS[args.model][1], 1024))
         else:
@@ -399,16 +399,13 @@ def main():
         """All quantized linears of one token.  Inputs come from fixed activation buffers (attention,
         norms and the element-wise glue between the linears are not part of the measured path)."""
         _keep[2].zero_()
-        fused = args.allreduce == "fused"
         for layer in model:
             for p in layer:
-                if fused and p["par"] == "row" and allreduce is not None:
-                    allreduce.bind_next()              # the launch below sums over the ranks in its finalizer
                 if on:
                     ext.dec_lutgemm(p["cfg"], xbuf[p["k"]], p["y"], p["qw"], p["alpha"], p["qb"], BITS, GROUP)
                 else:
                     ext.lutgemm_gemv(xbuf[p["k"]], p["y"], p["qw"], p["alpha"], p["qb"], BITS, GROUP)
-                if p["par"] == "row" and allreduce is not None and not fused:
+                if p["par"] == "row" and allreduce is not None:
                     allreduce(p["y"])
 
     def load_inputs(i):
@@ -580,7 +577,7 @@ def main():
         if cpu:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
-    if dist is not None and args.allreduce in ("push", "fused"):
+    if dist is not None and args.allreduce == "push":
         allreduce.check()          # raises if any wait for a peer ever ran out
     if dist is not None:
         # graphs that captured NCCL work must go before the communicator; leave without running

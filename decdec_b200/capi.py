@@ -65,7 +65,6 @@ SIGNATURES = {
     "decdec_tp_connect_ipc": (_i, [_up, _vp]),
     "decdec_tp_connect_ptrs": (_i, [_up, C.POINTER(_up)]),
     "decdec_tp_allreduce": (_i, [_up, _vp, _u32, _i, _vp]),
-    "decdec_tp_bind_next": (_i, [_up]),
     "decdec_tp_status": (_i, [_up, C.POINTER(_u32), C.POINTER(_u32)]),
     "decdec_tp_destroy": (_i, [_up]),
     "decdec_anyprec_dequant": (_i, [_vp, _vp, _vp, _u32, _u32, _i, _i, _vp]),

@@ -42,19 +42,6 @@ template <> struct Tr<BF16> {
     static __device__ __forceinline__ __nv_bfloat16 sub(__nv_bfloat16 a, __nv_bfloat16 b) { return __hsub(a, b); }
 };
 
-// Tensor-parallel exchange folded into the finalizer (world == 0: none).  The thread block that finalizes a tile
-// pushes the tile's fp32 partial sums into a slot of every rank's exchange buffer (plain peer stores), raises one
-// flag per (source rank, tile), waits - bounded - for the other ranks' flags of the same tile, sums the slots in
-// rank order and writes y: the all-reduce of a row-parallel projection without a second kernel.  Buffer layout
-// and call counter are those of the stand-alone exchange kernel (tp_allreduce.cu).
-struct TpFin {
-    unsigned char* peers[8];   // exchange buffers of all ranks (peers[rank] = own)
-    uint32_t world, rank;
-    uint32_t flags_off, slots_off, slot_stride;
-    uint32_t wait_polls;
-};
-constexpr uint32_t kTpFlagsPerRank = 64;
-
 // Output tiling and the accumulate/finalize state shared by the roles of one launch.
 struct FinParams {
     float* acc;            // [>= N] fp32, all zero between launches
@@ -67,7 +54,6 @@ struct FinParams {
     uint32_t tile_units;   // outputs per tile = 32 * tile_units
     uint32_t n_tiles;
     uint32_t expected;     // arrivals per tile before it is finalized
-    TpFin tp;              // exchange with the other tensor-parallel ranks at finalize time (world == 0: off)
 };
 
 // Arguments of the compensation (DEC) role.
@@ -191,87 +177,6 @@ __device__ __forceinline__ void finalize_span(const FinParams& f, uint32_t n0, u
     }
 }
 
-__device__ __forceinline__ void tp_st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t tp_ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-// finalize_span with the exchange: outputs [n0, n1) = tiles [t, t + run).  Called by ALL threads of the CTA
-// (it contains CTA barriers).  Needs N % 4 == 0 and a y aligned to four elements (the host checks both).
-template <int DT>
-__device__ __forceinline__ void finalize_span_tp(const FinParams& f, uint32_t t, uint32_t run, uint32_t n0, uint32_t n1,
-                                                 uint32_t nthreads, unsigned* s_flag) {
-    using T = typename Tr<DT>::T;
-    const TpFin& tp = f.tp;
-    T* y = reinterpret_cast<T*>(f.y);
-    const T* sc = reinterpret_cast<const T*>(f.scales);
-    const uint32_t wpr = f.N / 8;
-    unsigned char* mine = tp.peers[tp.rank];
-    const uint32_t e = *reinterpret_cast<volatile uint32_t*>(mine) + 1u;       // call number (advanced by the last CTA out)
-    const uint32_t half = e & 1u;
-    // 1. partial sums of this rank -> every rank's slot [half][rank]
-    const size_t my_slot = (size_t)tp.slots_off + ((size_t)half * tp.world + tp.rank) * tp.slot_stride;
-    for (uint32_t n = n0 + 4u * threadIdx.x; n < n1; n += 4u * nthreads) {
-        float4 v = __ldcg(reinterpret_cast<const float4*>(f.acc + n));
-        __stcg(reinterpret_cast<float4*>(f.acc + n), make_float4(0.f, 0.f, 0.f, 0.f));
-        if (f.acc2) {
-            const float4 r = __ldcg(reinterpret_cast<const float4*>(f.acc2 + n));
-            __stcg(reinterpret_cast<float4*>(f.acc2 + n), make_float4(0.f, 0.f, 0.f, 0.f));
-            const uint32_t w = n >> 3, nib = n & 7u;
-            v.x = fmaf(r.x, Tr<DT>::to_f(sc[(size_t)(nib + 0) * wpr + w]), v.x);
-            v.y = fmaf(r.y, Tr<DT>::to_f(sc[(size_t)(nib + 1) * wpr + w]), v.y);
-            v.z = fmaf(r.z, Tr<DT>::to_f(sc[(size_t)(nib + 2) * wpr + w]), v.z);
-            v.w = fmaf(r.w, Tr<DT>::to_f(sc[(size_t)(nib + 3) * wpr + w]), v.w);
-        }
-        v.x += Tr<DT>::to_f(y[n]); v.y += Tr<DT>::to_f(y[n + 1]); v.z += Tr<DT>::to_f(y[n + 2]); v.w += Tr<DT>::to_f(y[n + 3]);
-        for (uint32_t s = 0; s < tp.world; ++s)
-            *reinterpret_cast<float4*>(tp.peers[s] + my_slot + (size_t)n * 4u) = v;
-    }
-    __threadfence_system();
-    __syncthreads();
-    // 2. flags: one per (this rank, tile) in every other rank's buffer; then wait for theirs
-    const uint32_t nflag = run * (tp.world - 1u);
-    if (threadIdx.x == 0) *s_flag = 0u;
-    __syncthreads();
-    for (uint32_t i = threadIdx.x; i < nflag; i += nthreads) {
-        const uint32_t tile = t + i / (tp.world - 1u);
-        uint32_t s = i % (tp.world - 1u);
-        s += (s >= tp.rank) ? 1u : 0u;
-        tp_st_release_sys(reinterpret_cast<uint32_t*>(tp.peers[s] + tp.flags_off) + tp.rank * kTpFlagsPerRank + tile, e);
-    }
-    for (uint32_t i = threadIdx.x; i < nflag; i += nthreads) {
-        const uint32_t tile = t + i / (tp.world - 1u);
-        uint32_t s = i % (tp.world - 1u);
-        s += (s >= tp.rank) ? 1u : 0u;
-        const uint32_t* flag = reinterpret_cast<const uint32_t*>(mine + tp.flags_off) + s * kTpFlagsPerRank + tile;
-        uint32_t polls = 0, seen;
-        while ((int32_t)((seen = tp_ld_acquire_sys(flag)) - e) < 0) {
-            if (++polls >= tp.wait_polls) { atomicExch(s_flag, 1u); break; }
-            __nanosleep(64);
-        }
-        if ((int32_t)(seen - e) >= 2) atomicExch(s_flag, 1u);     // the peer ran ahead after a missed wait: slot not trustworthy
-    }
-    __syncthreads();
-    if (*s_flag) {
-        if (threadIdx.x == 0) atomicExch(reinterpret_cast<uint32_t*>(mine) + 2, 1u);
-        return;                                                   // y is left as it was
-    }
-    // 3. sum over ranks in rank order (bit-identical on every rank), single rounding
-    for (uint32_t n = n0 + 4u * threadIdx.x; n < n1; n += 4u * nthreads) {
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t s = 0; s < tp.world; ++s) {
-            const size_t off = (size_t)tp.slots_off + ((size_t)half * tp.world + s) * tp.slot_stride + (size_t)n * 4u;
-            const float4 q = __ldcg(reinterpret_cast<const float4*>(mine + off));
-            a.x += q.x; a.y += q.y; a.z += q.z; a.w += q.w;
-        }
-        y[n] = Tr<DT>::from_f(a.x); y[n + 1] = Tr<DT>::from_f(a.y); y[n + 2] = Tr<DT>::from_f(a.z); y[n + 3] = Tr<DT>::from_f(a.w);
-    }
-}
-
 // Arrive on tiles [t0, t1); the last arriver of a tile folds the accumulator into y.
 // Must be called by all threads of the CTA, after all its reductions into the accumulators were issued.
 // `nthreads` = number of threads of the CTA that take part (threads beyond it must have exited; the
@@ -303,23 +208,11 @@ __device__ __forceinline__ void arrive_and_finalize(const FinParams& f, uint32_t
                 const uint32_t t = tb + b0;
                 const uint32_t n0 = t * f.tile_units * 32u;
                 const uint32_t n1 = min(f.N, n0 + run * f.tile_units * 32u);
-                if (f.tp.world > 1u) finalize_span_tp<DT>(f, t, run, n0, n1, nthreads, s_flag);
-                else finalize_span<DT>(f, n0, n1, nthreads);
+                finalize_span<DT>(f, n0, n1, nthreads);
                 if (threadIdx.x < run) f.tickets[t + threadIdx.x] = 0u;
             }
         }
         __syncthreads();
-    }
-    if (f.tp.world > 1u && threadIdx.x == 0) {
-        // the thread block that leaves last advances the call counter of the exchange buffer
-        uint32_t* hdr = reinterpret_cast<uint32_t*>(f.tp.peers[f.tp.rank]);
-        const uint32_t e = *reinterpret_cast<volatile uint32_t*>(hdr) + 1u;
-        __threadfence();
-        if (atomicAdd(hdr + 1, 1u) + 1u == gridDim.x) {
-            hdr[1] = 0u;
-            __threadfence();
-            *reinterpret_cast<volatile uint32_t*>(hdr) = e;
-        }
     }
 }
 

@@ -203,7 +203,6 @@ int setup_fin(FinParams* f, const Workspace& ws, void* y, uint32_t N, uint32_t t
     f->err = ws.err;
     f->acc2 = nullptr;          // set by the callers that add a compensation role
     f->scales = nullptr;
-    memset(&f->tp, 0, sizeof(f->tp));
     f->y = y;
     f->N = N;
     f->tile_units = tile_units;
@@ -211,21 +210,6 @@ int setup_fin(FinParams* f, const Workspace& ws, void* y, uint32_t N, uint32_t t
     f->expected = expected;
     if (f->n_tiles > kTicketCap) return fail(DECDEC_E_UNSUPPORTED, "too many output tiles (%u)", f->n_tiles);
     return 0;
-}
-
-// decdec_tp_bind_next: the next GEMV entry point called on this host thread sums its output over the
-// tensor-parallel ranks of `comm` (inside its finalizer when the launch is eligible, else by the stand-alone
-// exchange kernel right after it).
-thread_local uintptr_t g_tp_next = 0;
-
-uintptr_t take_tp() {
-    const uintptr_t c = g_tp_next;
-    g_tp_next = 0;
-    return c;
-}
-
-int tp_after(uintptr_t comm, void* y, uint32_t N, int dtype, cudaStream_t s) {
-    return comm ? decdec_tp_allreduce(comm, y, N, dtype, s) : 0;
 }
 
 int run_dec_only(uintptr_t cfg_h, const void* x, void* y, uint32_t K, uint32_t N, int dtype, void* stream, bool fused_select) {
@@ -304,11 +288,9 @@ int run_bcq(Config* c, const void* x, void* y, const int32_t* qw, const void* al
         if (int r = fill_dec(c, x, true, f.n_tiles, &d)) return r;
         if (d.n_cta) { f.expected += d.n_rowparts; f.acc2 = ws.acc2; f.scales = d.scales; }
     }
-    uintptr_t tp = take_tp();
-    if (tp && tp_fill_fin(tp, N, f.n_tiles, y, dtype, &f.tp)) tp = 0;     // folded into the finalizer
     if (pipe) DD_CUDA(launch_bcq_pipe(dtype, g, d, f, geo, s));
     else DD_CUDA(launch_bcq(dtype, g, d, f, s));
-    return tp_after(tp, y, N, dtype, s);
+    return 0;
 }
 
 int run_anyprec(Config* c, const void* x, void* y, const int32_t* qw, uint32_t planes, const void* lut, uint32_t N,
@@ -347,12 +329,12 @@ int run_anyprec(Config* c, const void* x, void* y, const int32_t* qw, uint32_t p
     if (pipe) {
         g.direct = 0u;
         DD_CUDA(launch_anyprec_pipe(dtype, g, d, f, pgeo, s));
-        return tp_after(take_tp(), y, N, dtype, s);
+        return 0;
     }
     const bool fast3 = bits == 3 && (K % 128u) == 0u;
     if (anyprec_smem(K, fast3) > 200 * 1024) return fail(DECDEC_E_UNSUPPORTED, "anyprec: in_features %u too large for shared-memory staging", K);
     DD_CUDA(launch_anyprec(dtype, g, d, f, s));
-    return tp_after(take_tp(), y, N, dtype, s);
+    return 0;
 }
 
 int run_sqllm(Config* c, const void* x, void* y, const int32_t* qw, const void* lut, uint32_t N, uint32_t K, int bits,
@@ -379,7 +361,7 @@ int run_sqllm(Config* c, const void* x, void* y, const int32_t* qw, const void* 
     }
     g.direct = d.n_cta ? 0u : 1u;
     DD_CUDA(launch_sqllm(dtype, g, d, f, s));
-    return tp_after(take_tp(), y, N, dtype, s);
+    return 0;
 }
 
 // side stream + events for the dummy_* entry points, one set per device
@@ -596,11 +578,6 @@ int decdec_anyprec_dequant(const int32_t* qw, const void* lut, void* out, uint32
     if (K % 32u) return fail(DECDEC_E_INVALID, "in_features must be a multiple of 32, got %u", K);
     DD_CUDA(launch_ap_dequant(dtype, reinterpret_cast<const uint32_t*>(qw), lut, out, N, K, (uint32_t)bits,
                               reinterpret_cast<cudaStream_t>(stream)));
-    return 0;
-}
-
-int decdec_tp_bind_next(uintptr_t comm) {
-    g_tp_next = comm;
     return 0;
 }
 

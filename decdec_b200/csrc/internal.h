@@ -26,7 +26,6 @@ cudaError_t launch_bcq_dequant(int dt, const uint32_t* qweight, const void* alph
 cudaError_t launch_burner(int blocks, long long iters, cudaStream_t s);
 
 int set_last_error(int code, const char* msg);
-bool tp_fill_fin(uintptr_t comm, uint32_t N, uint32_t n_tiles, const void* y, int dtype, TpFin* out);
 size_t dec_only_smem();
 size_t anyprec_smem(uint32_t K, bool fast3);
 size_t sqllm_smem(uint32_t K);

@@ -20,7 +20,6 @@
 #include "../../include/decdec_b200.h"
 
 #include <cstdio>
-#include <cstring>
 #include <mutex>
 
 namespace {
@@ -103,7 +102,6 @@ extern "C" int decdec_lutgemm_gemv_noalloc(const void* x, void* y, const int32_t
     f.tickets = reinterpret_cast<unsigned*>(scratch + kAccBytes);
     f.err = f.tickets + kMaxTiles;
     f.acc2 = nullptr;       // no compensation role on this path
-    memset(&f.tp, 0, sizeof(f.tp));
     f.scales = nullptr;
     f.y = y;
     f.N = N;

@@ -26,7 +26,7 @@ namespace {
 using namespace dd;
 
 constexpr uint32_t kTpMaxWorld = 8;
-constexpr uint32_t kTpMaxCta = kTpFlagsPerRank;     // flags per source rank (thread blocks of the exchange kernel, or output tiles)
+constexpr uint32_t kTpMaxCta = 64;
 constexpr uint32_t kTpThreads = 256;
 constexpr size_t kTpHdr = 256;                                     // [epoch, ticket, err, pad]
 
@@ -163,25 +163,6 @@ int tp_fail(int code, const char* fmt, const char* detail = "") {
 }
 
 }  // namespace
-
-namespace dd {
-
-// Exchange folded into a GEMV launch's finalizer (common.cuh: finalize_span_tp).  False = not eligible, the caller
-// runs the stand-alone exchange kernel after its launch instead.
-bool tp_fill_fin(uintptr_t comm, uint32_t N, uint32_t n_tiles, const void* y, int dtype, TpFin* out) {
-    TpComm* c = reinterpret_cast<TpComm*>(comm);
-    if (!c || !c->connected || c->world < 2) return false;
-    const uint32_t esz = dtype == FP32 ? 4 : 2;
-    if (N > c->max_n || (N & 3u) || n_tiles > kTpMaxCta || (reinterpret_cast<uintptr_t>(y) & (4u * esz - 1u))) return false;
-    memset(out, 0, sizeof(*out));
-    for (uint32_t s = 0; s < c->world; ++s) out->peers[s] = c->peers[s];
-    out->world = c->world; out->rank = c->rank;
-    out->flags_off = (uint32_t)c->L.flags_off; out->slots_off = (uint32_t)c->L.slots_off; out->slot_stride = c->L.slot_stride;
-    out->wait_polls = c->wait_polls;
-    return true;
-}
-
-}  // namespace dd
 
 extern "C" {
 

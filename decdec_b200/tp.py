@@ -158,12 +158,6 @@ class PushAllReduce:
         self._capi.call("decdec_tp_allreduce", self._comm, y.data_ptr(), y.numel(), self._DT[y.dtype], stream)
         return y
 
-    def bind_next(self) -> None:
-        """The next GEMV entry point called on this thread (lutgemm_gemv, dec_lutgemm, ...) leaves the sum over the ranks
-        in its output.  Binary-coded launches fold the exchange into their finalizer (no second kernel); others run
-        the exchange kernel right after the GEMV."""
-        self._capi.call("decdec_tp_bind_next", self._comm)
-
     def status(self):
         calls, err = self._C.c_uint32(0), self._C.c_uint32(0)
         self._capi.call("decdec_tp_status", self._comm, self._C.byref(calls), self._C.byref(err))

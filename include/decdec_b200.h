@@ -135,10 +135,6 @@ int decdec_lutgemm_dequant(const int32_t* qweight, const void* alpha, const void
  *   decdec_tp_status       calls completed and the error word (1 = a wait ran out: a peer did not arrive
  *                          within DECDEC_TP_WAIT_POLLS polls, default 2^21, about a second; y was left unsummed).
  *   decdec_tp_layout       byte offsets inside an exchange buffer (flags [world][64] u32, slots [2][world][stride]).
- *   decdec_tp_bind_next    the next GEMV entry point (lutgemm/anyprec/sqllm, with or without compensation) called on this
- *                          host thread leaves the SUM over the ranks in y.  Binary-coded launches fold the exchange into
- *                          the kernel: the thread block that finalizes an output tile pushes the tile's fp32 sums to the
- *                          peers, waits for theirs and rounds once; other launches run decdec_tp_allreduce after the GEMV.
  */
 int decdec_tp_layout(uint32_t world, uint32_t max_n, size_t* flags_off, size_t* slots_off, size_t* slot_stride, size_t* bytes);
 int decdec_tp_create(uint32_t world, uint32_t rank, uint32_t max_n, uintptr_t* comm_out, unsigned char* ipc_handle_out);
@@ -146,7 +142,6 @@ int decdec_tp_local_ptr(uintptr_t comm, void** ptr_out);
 int decdec_tp_connect_ipc(uintptr_t comm, const unsigned char* handles);
 int decdec_tp_connect_ptrs(uintptr_t comm, const uintptr_t* peer_ptrs);
 int decdec_tp_allreduce(uintptr_t comm, void* y_dev, uint32_t n, int dtype, void* stream);
-int decdec_tp_bind_next(uintptr_t comm);
 int decdec_tp_status(uintptr_t comm, uint32_t* calls_out, uint32_t* error_out);
 int decdec_tp_destroy(uintptr_t comm);
 

@@ -105,72 +105,6 @@ def test_staged_peers_sum_in_rank_order(capi, dtype, world, rank):
     capi.call("decdec_tp_destroy", comm)
 
 
-@pytest.mark.parametrize("with_dec", [False, True])
-def test_exchange_folded_into_the_gemv_finalizer(capi, with_dec):
-    """decdec_tp_bind_next + a binary-coded GEMV: the finalizing thread blocks push fp32 tile sums, wait for the
-    (staged) peer's, and round once.  World of two, this process is rank 0; the peer's sums and flags are staged."""
-    import numpy as np
-    from decdec_b200 import ops
-    from oracle import forward as ofw
-    from tests import problems as P
-    N, K, world, rank, max_n = 4096, 2048, 2, 0, 8192
-    flags_off, slots_off, stride, nbytes = _layout(capi, world, max_n)
-    comm, ptr = _create(capi, world, rank, max_n)
-    mine = torch.as_tensor(_Raw(ptr, nbytes), device="cuda")
-    peer = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
-    capi.call("decdec_tp_connect_ptrs", comm, (C.c_size_t * 2)(ptr, peer.data_ptr()))
-    L = P.bcq_layer(N, K, 3, 128, seed=5)
-    x = P.make_activation(K, seed=6)
-    own = ofw.layer_output(L["w_hat"], P.to_np(x))
-    cfg = None
-    if with_dec:
-        cs, rs = P.random_residual(N, K, seed=7)
-        thr = P.make_thresholds(K)
-        rows = torch.zeros(4096, dtype=torch.int32, device="cuda")
-        acts = torch.zeros(4096, dtype=torch.float16, device="cuda")
-        ctx = ops.create_dec_context(8, rows, acts)
-        cfg = ops.create_dec_config(ctx, 8, cs, rs, thr)
-        er, ea, _ = P.expected_selection(x, thr, 8, "fp16")
-        own = own + ofw.dec_delta(P.to_np(x), er, cs.numpy(), P.to_np(rs), ea)
-    qw, al, qb = L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda()
-    g = torch.Generator(device="cuda").manual_seed(11)
-    for call in (1, 2):
-        half = call & 1
-        other = torch.randn(N, device="cuda", generator=g)                        # the peer's fp32 partial sums
-        off = slots_off + (half * world + 1) * stride
-        mine[off:off + N * 4].view(torch.float32).copy_(other)
-        mine[flags_off:flags_off + world * 64 * 4].view(torch.int32).view(world, 64)[1, :] = call
-        y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
-        torch.cuda.synchronize()
-        capi.call("decdec_tp_bind_next", comm)
-        if with_dec:
-            ops.dec_lutgemm(cfg, x.cuda(), y, qw, al, qb, 3, 128)
-        else:
-            ops.lutgemm_gemv(x.cuda(), y, qw, al, qb, 3, 128)
-        torch.cuda.synchronize()
-        assert _status(capi, comm) == (call, 0)
-        ref = own + other.double().cpu().numpy()
-        err = np.abs(y.float().cpu().numpy().reshape(-1) - ref)
-        assert err.max() <= 1e-2 and np.linalg.norm(err) / np.linalg.norm(ref) <= 1e-3
-        # this rank's fp32 sums reached the peer's buffer, with one flag per output tile
-        off0 = slots_off + (half * world + 0) * stride
-        pushed = peer[off0:off0 + N * 4].view(torch.float32).double().cpu().numpy()
-        assert np.abs(pushed - own).max() <= 1e-2
-        fl = peer[flags_off:flags_off + world * 64 * 4].view(torch.int32).view(world, 64)[0]
-        n_set = int((fl == call).sum())
-        assert 1 <= n_set <= 64 and bool((fl[:n_set] == call).all())
-    # an unbound call afterwards is a plain GEMV again
-    y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
-    ops.lutgemm_gemv(x.cuda(), y, qw, al, qb, 3, 128)
-    torch.cuda.synchronize()
-    base = ofw.layer_output(L["w_hat"], P.to_np(x))
-    assert np.abs(y.float().cpu().numpy().reshape(-1) - base).max() <= 1e-2
-    assert _status(capi, comm)[0] == 2
-    if cfg is not None:
-        ops.destroy_dec_config(cfg)
-    capi.call("decdec_tp_destroy", comm)
-
-
 def test_wait_runs_out_and_context_survives(capi):
     os.environ["DECDEC_TP_WAIT_POLLS"] = "2000"          # a few milliseconds
     try:
@@ -250,34 +184,8 @@ def _rank_main(rank, world, port, q):
             gr.replay()
             s.synchronize()
             ok &= bool(torch.equal(yb, ref.half()))
-    # exchange folded into a row-parallel binary-coded GEMV (each rank holds half of K)
-    from decdec_b200 import ops
-    Kl, N = 2048, 4096
-    gw = torch.Generator(device=dev).manual_seed(500 + rank)
-    qw = torch.randint(-2**31, 2**31 - 1, (Kl // 32, 3, N), dtype=torch.int32, device=dev, generator=gw)
-    al = (torch.rand(Kl // 128, 3, N, device=dev, generator=gw) * 0.01).half()
-    qb = ((torch.rand(Kl // 128, N, device=dev, generator=gw) - 0.5) * 0.01).half()
-    fused_calls = 0
-    for i in range(3):
-        xl = torch.randn(1, 1, Kl, device=dev, generator=gw).half()
-        part = torch.zeros(1, 1, N, dtype=torch.float16, device=dev)
-        ops.lutgemm_gemv(xl, part, qw, al, qb, 3, 128)
-        ref = part.float().clone()
-        dist.all_reduce(ref)
-        yf = torch.zeros(1, 1, N, dtype=torch.float16, device=dev)
-        ar.bind_next()
-        ops.lutgemm_gemv(xl, yf, qw, al, qb, 3, 128)
-        torch.cuda.synchronize()
-        fused_calls += 1
-        d = (yf.float() - ref).abs()
-        ok &= bool(d.max() <= 2e-2) and bool(d.norm() / ref.norm() <= 2e-3)
-        # every rank holds the same bits
-        both = [torch.empty_like(yf) for _ in range(world)]
-        dist.all_gather(both, yf)
-        ok &= bool(torch.equal(both[0], both[1]))
     ar.check()
     calls, err = ar.status()
-    calls -= fused_calls
     dist.barrier()
     torch.cuda.synchronize()
     q.put((rank, ok, calls, err))

@@ -46,6 +46,8 @@ _vp, _u32, _i, _up, _ll = C.c_void_p, C.c_uint32, C.c_int, C.c_size_t, C.c_longl
 SIGNATURES = {
     "decdec_last_error": (C.c_char_p, []),
     "decdec_compiled_arch": (_i, []),
+    "decdec_stream_status": (_i, [_vp, C.POINTER(_u32)]),
+    "decdec_stream_reset": (_i, [_vp]),
     "decdec_create_context": (_i, [_u32, _vp, _vp, _u32, _i, C.POINTER(_up)]),
     "decdec_destroy_context": (_i, [_up]),
     "decdec_create_config": (_i, [_up, _u32, _vp, _i, _u32, _u32, _vp, _i, _vp, _i, C.POINTER(_up)]),

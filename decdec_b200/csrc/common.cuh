@@ -93,6 +93,13 @@ __device__ __forceinline__ uint32_t ldg_stream(const uint32_t* p) {
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// The error word of a workspace lives in mapped host memory (the host reads it before every call without a copy):
+// a plain store plus a system-scope fence, never an atomic.
+__device__ __forceinline__ void raise_error(unsigned* err, unsigned code) {
+    *reinterpret_cast<volatile unsigned*>(err) = code;
+    __threadfence_system();
+}
+
 // explicit shared-window load (the table lookups must not degrade to generic loads)
 __device__ __forceinline__ float lds_f32(uint32_t saddr) {
     float v;

@@ -6,6 +6,10 @@
 // the R LUT rows.  A producer thread moves them with four 1-D bulk asynchronous copies
 // (cp.async.bulk, 6-8 KB each, completion counted on an mbarrier) several stages ahead of sixteen
 // consumer warps; a warp's work item is (row of the stage, 4096-channel segment of that row).
+// A CTA owns its rows completely (all of K), so the row sums meet in a small shared-memory buffer and the
+// CTA folds them into y itself: GEMV-only launches use no global accumulator, ticket or fence.  Fused
+// launches store the sums into the workspace accumulator and arrive on the tile's ticket, where they meet
+// the compensation CTAs.
 // Requirements: bits == 3, K % 128 == 0, K <= 32768.  Every mbarrier wait is bounded.
 #pragma once
 #include "gemv_anyprec.cuh"
@@ -22,7 +26,10 @@ struct ApPipeGeom {
     uint32_t stage_bytes;
     uint32_t x_bytes;          // staged activations (rounded to 128)
     uint32_t rows_per_cta;     // multiple of R
+    uint32_t part_bytes;       // row sums of the CTA (fp32, rounded to 128 bytes)
     uint32_t smem_bytes;
+    uint32_t direct;           // 1: fold into y; 0: store into the accumulator and take the tile's ticket
+    uint32_t wait_ns;          // limit of one mbarrier wait (DECDEC_PIPE_WAIT_NS)
 };
 
 constexpr int kApPipeHdr = 256;   // [abort, flag][full barriers 8][empty barriers 8]
@@ -36,7 +43,8 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
     const uint32_t bar_full = smem_u32(sm + 64);
     const uint32_t bar_empty = bar_full + 64;
     T* sx = reinterpret_cast<T*>(sm + kApPipeHdr);
-    unsigned char* stage0 = sm + kApPipeHdr + geo.x_bytes;
+    float* part = reinterpret_cast<float*>(sm + kApPipeHdr + geo.x_bytes);
+    unsigned char* stage0 = sm + kApPipeHdr + geo.x_bytes + geo.part_bytes;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t nwords = p.K / 32;
@@ -56,6 +64,7 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    for (uint32_t i = tid; i < geo.rows_per_cta; i += kApPipeThreads) part[i] = 0.0f;
     __syncthreads();
 
     if (warp == 16) {
@@ -66,7 +75,7 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
             uint32_t issued = 0;
             for (uint32_t i = 0; i < nst; ++i) {
                 const uint32_t s = i % S, use = i / S;
-                if (use > 0 && !mbar_wait(bar_empty + 8 * s, (use - 1) & 1u, s_abort)) break;
+                if (use > 0 && !mbar_wait(bar_empty + 8 * s, (use - 1) & 1u, s_abort, geo.wait_ns)) break;
                 const uint32_t n0 = r0 + i * R;
                 const uint32_t rows = min(R, r1 - n0);
                 const uint32_t full = bar_full + 8 * s;
@@ -82,7 +91,7 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
                 const uint32_t first = issued > S ? issued - S : 0;
                 for (uint32_t i = first; i < issued; ++i) {
                     volatile uint32_t never = 0;
-                    mbar_wait(bar_full + 8 * (i % S), (i / S) & 1u, &never);
+                    mbar_wait(bar_full + 8 * (i % S), (i / S) & 1u, &never, 1000000000u);
                 }
             }
         }
@@ -103,7 +112,7 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
 
         for (uint32_t i = 0; i < nst; ++i) {
             const uint32_t s = i % S;
-            if (!mbar_wait(bar_full + 8 * s, (i / S) & 1u, s_abort)) break;
+            if (!mbar_wait(bar_full + 8 * s, (i / S) & 1u, s_abort, geo.wait_ns)) break;
             const unsigned char* st = stage0 + (size_t)s * geo.stage_bytes;
             const uint32_t n = r0 + i * R + row_in_stage;
             float facc = 0.0f;
@@ -165,15 +174,59 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
             if (lane == 0) mbar_arrive(bar_empty + 8 * s);      // stage words are in registers
 #pragma unroll
             for (int d = 16; d >= 1; d >>= 1) facc += __shfl_xor_sync(0xffffffffu, facc, d);
-            if (lane == 0 && has_item && n < r1) atomicAdd(&f.acc[n], facc);
+            if (lane == 0 && has_item && n < r1) {
+                if (geo.segs == 1) part[n - r0] = facc;           // one warp per row: nobody else writes it
+                else atomicAdd(&part[n - r0], facc);              // the K segments of a row meet here
+            }
         }
     }
     if (warp == 16) pdl_wait();     // the producer warp touches the accumulator and y only from here on
+    // fold the CTA's rows: four consecutive outputs per thread; y is read before the barrier so that the
+    // load overlaps the last warps' work
+    T* y = reinterpret_cast<T*>(f.y);
+    const uint32_t nrows = r1 - r0;
+    const bool yvec = geo.direct && (nrows & 3u) == 0u && (r0 & 3u) == 0u &&
+                      (reinterpret_cast<uintptr_t>(f.y) & (4u * sizeof(T) - 1u)) == 0u;
+    float y0[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool pre = yvec && 4u * (uint32_t)tid < nrows;
+    if (pre) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(y + r0 + 4u * tid);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) y0[i] = Tr<DT>::to_f(e[i]);
+    }
     __syncthreads();
-    if (*s_abort) {
-        if (tid == 0) atomicExch(f.err, 1u);
+    if (*s_abort && tid == 0) raise_error(f.err, 1u);
+    if (geo.direct) {
+        if (!*s_abort) {            // an unfinished launch leaves y alone
+            if (yvec) {
+                for (uint32_t i = 4u * tid; i < nrows; i += 4u * kApPipeThreads) {
+                    const float4 v = *reinterpret_cast<const float4*>(part + i);
+                    float o[4];
+                    if (pre && i == 4u * (uint32_t)tid) { o[0] = y0[0]; o[1] = y0[1]; o[2] = y0[2]; o[3] = y0[3]; }
+                    else {
+                        const uint2 raw = *reinterpret_cast<const uint2*>(y + r0 + i);
+                        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) o[q] = Tr<DT>::to_f(e[q]);
+                    }
+                    o[0] += v.x; o[1] += v.y; o[2] += v.z; o[3] += v.w;
+                    uint2 raw;
+                    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) e[q] = Tr<DT>::from_f(o[q]);
+                    *reinterpret_cast<uint2*>(y + r0 + i) = raw;
+                }
+            } else {
+                for (uint32_t i = tid; i < nrows; i += kApPipeThreads)
+                    y[r0 + i] = Tr<DT>::from_f(Tr<DT>::to_f(y[r0 + i]) + part[i]);
+            }
+        }
         return;
     }
+    // fused launch: the sums go to the accumulator (this CTA is their only GEMV writer) and the CTA arrives on its
+    // tile even after a failed wait, so that the workspace stays consistent
+    for (uint32_t i = tid; i < nrows; i += kApPipeThreads) __stcg(f.acc + r0 + i, part[i]);
     arrive_and_finalize<DT>(f, cta, cta + 1, s_flag, kApPipeThreads);
 }
 

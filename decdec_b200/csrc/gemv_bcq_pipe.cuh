@@ -5,15 +5,31 @@
 // through registers: a producer thread moves a tile of [16 k-rows x bits planes] x 128 outputs (+ the
 // alpha and q_bias rows that go with them) per stage from HBM to shared memory with three tiled TMA
 // copies (cp.async.bulk.tensor.2d, completion counted on an mbarrier), several stages ahead of the
-// consumer warps (three groups of eight, taking stages round-robin).  HBM latency is then covered by bytes in flight (about 29 KB per stage, up to
-// 5 stages per SM) instead of by occupancy.  The tile lands densely (512-byte lines); the lanes of a
-// warp read it in a skewed order (k-row j reads the 16-byte groups (j + c) mod 8 and +4), so every
-// 128-bit shared load of a quarter warp touches eight different bank groups.
+// consumer warps (three groups of eight, taking stages round-robin).  HBM latency is then covered by
+// bytes in flight (about 29 KB per stage, up to 5 stages per SM) instead of by occupancy.  The tile
+// lands densely (512-byte lines); the lanes of a warp read it in a skewed order (k-row j reads the
+// 16-byte groups (j + c) mod 8 and +4), so every 128-bit shared load of a quarter warp touches eight
+// different bank groups.
+//
+// Split of the work.  The K dimension is cut into 512-channel slices (one 64 KB table block each); a CTA is
+// (K slice, output tile) and the CTAs of a tile are neighbours in the grid.  After every stage a lane adds its
+// 32-channel-row total into the fp32 accumulator of the workspace (red.global, fire and forget).  How a tile is
+// finished depends on the launch:
+//  * GEMV-only launches: the CTA of the LAST K slice of a tile is its finalizer.  The others publish their sums
+//    (fence, one release increment of the tile's counter) and leave; the finalizer, which the hardware dispatched
+//    after them, polls the counter (bounded) and folds the accumulator into y.  Nobody pays an atomic round trip.
+//  * fused launches (compensation CTAs in the same grid, which finish late): every CTA takes a ticket and the last
+//    arriver folds (common.cuh), so no CTA spins while the host link is busy.
+// Thread-block clusters with a reduction through distributed shared memory were built and measured for this split
+// and lost: only 15 clusters of 8 CTAs with this shared-memory footprint are resident at once (120 of 148 SMs),
+// cluster placement delays the early start that programmatic dependent launch gives, and walking several K slices
+// per CTA costs about 1.5 us per table rebuild.
 //
 // Requirements (otherwise the register-staged kernel of gemv_bcq.cuh runs): N % 128 == 0,
 // K % 512 == 0, group size one of 32..512 dividing 512, at least two stages fit in shared memory.
-// Every wait on an mbarrier is bounded; on expiry the CTA raises the error word of the workspace
-// and leaves without touching the output.
+// Every wait (mbarrier, tile counter) is bounded; on expiry the CTA raises the error word of the workspace, still
+// takes part in the counter / ticket protocol (so that the workspace stays consistent) and the caller reads the
+// error through decdec_stream_status.
 #pragma once
 #include "common.cuh"
 #include "gemv_bcq.cuh"
@@ -24,21 +40,20 @@ namespace dd {
 
 constexpr int kPipeStageN = 128;            // outputs per stage
 constexpr int kPipeLine = 512;              // bytes of one [k-row, plane] line of a stage (128 outputs)
-#ifndef DD_GROUPS
-#define DD_GROUPS 3
-#endif
-constexpr int kPipeGroups = DD_GROUPS;       // consumer groups of 8 warps, taking stages round-robin
+constexpr int kPipeGroups = 3;              // consumer groups of 8 warps, taking stages round-robin
 constexpr int kPipeThreads = kPipeGroups * 256 + 32;   // + 1 producer warp
-constexpr uint32_t kPipeWaitLimit = 1u << 20;    // polls per wait before the CTA gives up
-constexpr uint32_t kPipeSuspendNs = 100000u;     // a poll may sleep this long in hardware (wakes early on completion)
+constexpr uint32_t kPipeSuspendNs = 20000u;      // a poll may sleep this long in hardware (wakes early on completion)
 
 struct PipeGeom {
     uint32_t stages;         // pipeline depth S
     uint32_t stage_bytes;    // bytes of one stage in shared memory
     uint32_t w_bytes;        // weight part of a stage
     uint32_t a_bytes;        // alpha part of a stage
-    uint32_t tile_stages;    // stages (128 outputs each) per CTA
+    uint32_t tile_stages;    // stages (128 outputs each) per output tile
     uint32_t smem_bytes;     // dynamic shared memory of the launch
+    uint32_t poll;           // 1: GEMV-only launch, the CTA of the last K slice polls the tile's counter and folds
+    uint32_t wait_ns;        // limit of one bounded wait (DECDEC_PIPE_WAIT_NS)
+    uint32_t test_skip_last; // test hook: the producer withholds its last stage, so that a wait runs out
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -61,11 +76,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity), "r"(kPipeSuspendNs) : "memory");
     return ok != 0;
 }
-// bounded wait: false if the barrier did not flip within the limit or another thread gave up
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
-    for (uint32_t i = 0; i < kPipeWaitLimit; ++i) {
+// bounded wait: false if the barrier did not flip within about `limit_ns` or another thread of the CTA gave up.
+// The bound is kept on the SM's own cycle counter (cheap to read; two cycles per nanosecond at the top clock).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t limit_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    const long long limit = 2ll * (long long)limit_ns;
+    for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 63u && *abort_flag) return false;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > limit) break;
     }
     *abort_flag = 1u;
     return false;
@@ -78,6 +98,9 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 __device__ __forceinline__ void tma_2d_g2s(uint32_t dst, const CUtensorMap* map, uint32_t x, uint32_t y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
 struct PipeMaps {
@@ -105,8 +128,8 @@ __device__ __forceinline__ void lds4f(const unsigned char* base, uint32_t elem, 
 
 // Shared memory.  The 64 KB of tables start at the first shared-window address that is a multiple of
 // 64 KB, so that a lookup address {entry byte, slot offset} is complete after ONE byte-permute (bits
-// 16.. of the address come from a constant byte); the pipeline stages fill the space before and after:
-//   [header 256 B: rowsum, flags, 8 full + 8 empty barriers][stages ...][tables @ 64 KB multiple][stages ...]
+// 16.. of the address come from two constant bytes); the pipeline stages fill the space before and after:
+//   [header 256 B: row sums, flags, 8 full + 8 empty barriers][stages ...][tables @ 64 KB multiple][stages ...]
 constexpr int kPipeHdr = 256;
 constexpr uint32_t kPipeTblOffAssumed = 65536 - 1024;   // dynamic shared memory normally starts 1 KB into the window
 
@@ -115,11 +138,41 @@ __host__ __device__ inline uint32_t pipe_stages_before(uint32_t tbl_off, uint32_
     return tbl_off > (uint32_t)kPipeHdr ? (tbl_off - kPipeHdr) / stage_bytes : 0u;
 }
 
+// activations of one (k-row, byte) table slot: 8 consecutive channels
+template <int DT>
+__device__ __forceinline__ void pipe_load_x8(const void* xbase, uint32_t k0, bool vec, float* xv) {
+    using T = typename Tr<DT>::T;
+    const T* x = reinterpret_cast<const T*>(xbase);
+    if (vec) {
+        if constexpr (DT == FP32) {
+            const float4 a = *reinterpret_cast<const float4*>(x + k0);
+            const float4 b = *reinterpret_cast<const float4*>(x + k0 + 4);
+            xv[0] = a.x; xv[1] = a.y; xv[2] = a.z; xv[3] = a.w; xv[4] = b.x; xv[5] = b.y; xv[6] = b.z; xv[7] = b.w;
+        } else {
+            const uint4 raw = *reinterpret_cast<const uint4*>(x + k0);
+            const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) xv[i] = Tr<DT>::to_f(e[i]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xv[i] = Tr<DT>::to_f(x[k0 + i]);
+    }
+}
+
+// acquire load of a tile counter
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 template <int DT, int BITS>
 __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const PipeGeom& geo, const PipeMaps& maps,
                               uint32_t cta, unsigned char* sm) {
     using T = typename Tr<DT>::T;
     constexpr uint32_t ESZ = (DT == FP32) ? 4u : 2u;
+    constexpr uint32_t NCONS = kPipeGroups * 256;
     const uint32_t sm_base = smem_u32(sm);
     const uint32_t tbl_off = (65536u - (sm_base & 65535u)) & 65535u;     // tables at a 64 KB multiple of the window
     float* tbl = reinterpret_cast<float*>(sm + tbl_off);
@@ -144,20 +197,15 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
     const uint32_t st0 = tile * geo.tile_stages;
     const uint32_t nst = min(geo.tile_stages, nst_total - st0);
     const uint32_t S = geo.stages;
-    const uint32_t groups = kBcqSlice / p.group;      // scale groups inside the K slice
+    const uint32_t groups = kBcqSlice / p.group;        // scale groups inside the K slice
 
-    {
-        // the host sized the launch for the usual window offset; refuse to run past the allocation
+    if (tid == 0) {
+        // the host sized the launch for the usual window offset; never run past the allocation
         uint32_t dyn;
         asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
         const uint32_t after = S > n_before ? S - n_before : 0u;
-        if (tbl_off + kBcqTableBytes + after * geo.stage_bytes > dyn || (tbl_off & 127u)) {
-            if (tid == 0) atomicExch(f.err, 2u);
-            return;
-        }
-    }
-    if (tid == 0) {
-        *s_abort = 0u;
+        const bool bad = tbl_off + kBcqTableBytes + after * geo.stage_bytes > dyn || (tbl_off & 127u);
+        *s_abort = bad ? 2u : 0u;
         for (uint32_t s = 0; s < S; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 8);
@@ -168,16 +216,16 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
 
     if (warp == kPipeGroups * 8) {
         // ------------------------------ producer warp (one elected lane) -------------------------
-        const uint32_t tx = geo.w_bytes + geo.a_bytes + groups * kPipeStageN * ESZ;
-        uint32_t issued = 0;
-#if defined(DD_EXP) && DD_EXP == 2
-        if (false) {      // compute only: nothing is streamed, consumers read whatever shared memory holds
-#else
-        if (lane == 0) {
-#endif
-            for (uint32_t i = 0; i < nst; ++i) {
+        if (lane == 0 && !*s_abort) {
+            const uint32_t tx = geo.w_bytes + geo.a_bytes + groups * kPipeStageN * ESZ;
+            const uint32_t n_issue = (geo.test_skip_last && nst) ? nst - 1u : nst;
+            uint32_t issued = 0;
+            tma_prefetch_desc(&maps.w);
+            tma_prefetch_desc(&maps.a);
+            tma_prefetch_desc(&maps.b);
+            for (uint32_t i = 0; i < n_issue; ++i) {
                 const uint32_t s = i % S, use = i / S;
-                if (use > 0 && !mbar_wait(bar_empty + 8 * s, (use - 1) & 1u, s_abort)) break;
+                if (use > 0 && !mbar_wait(bar_empty + 8 * s, (use - 1) & 1u, s_abort, geo.wait_ns)) break;
                 const uint32_t full = bar_full + 8 * s;
                 mbar_expect_tx(full, tx);
                 const uint32_t n0 = (st0 + i) * kPipeStageN;
@@ -192,24 +240,52 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
                 const uint32_t first = issued > S ? issued - S : 0;
                 for (uint32_t i = first; i < issued; ++i) {
                     volatile uint32_t never = 0;
-                    mbar_wait(bar_full + 8 * (i % S), (i / S) & 1u, &never);
+                    mbar_wait(bar_full + 8 * (i % S), (i / S) & 1u, &never, 1000000000u);
                 }
             }
         }
+        pdl_wait();
     } else {
-        // ------------------------------ consumer warps (8) ---------------------------------------
-        // build the 64 subset-sum tables of the slice: slot = (krow / 8) * 32 + (krow % 8) * 4 + byte;
-        // a thread fills the 32 entries whose bits 5..7 equal warp / 2
-        pdl_wait();     // weights are already streaming (producer warp); activations come from earlier kernels
-        if (warp < 16) {
-            const uint32_t slot = (warp & 1) * 32 + lane;
-            const uint32_t qe = warp >> 1;
-            const uint32_t krow_b = (slot >> 5) * 8 + ((slot & 31) >> 2);
-            const uint32_t k0 = kbase + 32 * krow_b + 8 * (slot & 3);
-            const T* x = reinterpret_cast<const T*>(p.x);
-            float xv[8];
+        // ------------------------------ consumer warps (3 groups of 8) ---------------------------
+        // Everything that does not depend on memory is prepared before the wait for the previous kernel.
+        // table slot = (krow / 8) * 32 + (krow % 8) * 4 + byte; a building thread fills the 32 entries whose
+        // bits 5..7 equal warp / 2, for its slot
+        const bool builder = warp < 16;
+        const uint32_t slot = (warp & 1) * 32 + lane;
+        const uint32_t qe = warp >> 1;
+        const uint32_t krow_b = (slot >> 5) * 8 + ((slot & 31) >> 2);
+        const uint32_t koff = 32 * krow_b + 8 * (slot & 3);
+        const bool xvec = (reinterpret_cast<uintptr_t>(p.x) & 15u) == 0u;
+        // main loop: warp = (k half, 32-output block); lane = (k-row j, c).  Row j reads the 16-byte groups
+        // tA = (j + c) & 7 and tB = tA ^ 4 of the block's 128-byte line segment.
+        const uint32_t j = lane & 7, c = lane >> 3;
+        const uint32_t grp = warp >> 3;
+        const uint32_t blk = warp & 3, khalf = (warp >> 2) & 1;
+        const uint32_t krow = khalf * 8 + j;
+        const uint32_t tA = (j + c) & 7, tB = tA ^ 4;
+        uint32_t sel[4], lb[4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) xv[i] = Tr<DT>::to_f(x[k0 + i]);
+        for (int s = 0; s < 4; ++s) {
+            const uint32_t byte = (s + c) & 3;
+            sel[s] = 0x6504u | (byte << 4);                // result bytes = {lb.b0, word.byte[byte], lb.b1, lb.b2}
+            // b0 = slot offset inside a 256-byte entry row, b1 and b2 = bits 16..31 of the tables' window address
+            lb[s] = (khalf * 128 + (4 * j + byte) * 4) | (((smem_u32(tbl) >> 16) & 0xffffu) << 8);
+        }
+        const uint32_t g = (32 * krow) / p.group;          // scale group of this lane's k-row inside the slice
+        const uint32_t nA = blk * 32 + 4 * tA, nB = blk * 32 + 4 * tB;
+        // partner lanes of the reduction over k-rows (lanes sharing (j + c) & 3 hold the same two groups)
+        const uint32_t p4 = lane ^ 4, p2 = lane ^ 18;
+        const uint32_t p1 = (j ^ 1) + 8 * (((j & 1) ? c + 1 : c + 3) & 3);
+        const bool swapAB = (tA & 4) != 0;                  // after the swap X = group r, Y = group r + 4, r = tA & 3
+        const uint32_t r4 = tA & 3;
+        const uint32_t n_out = blk * 32 + ((j & 4) ? 16 : 0) + 4 * r4 + (j & 3);
+        float* acc_lane = f.acc + (size_t)st0 * kPipeStageN + n_out;
+
+        pdl_wait();     // weights are already streaming (producer warp); activations come from earlier kernels
+        DD_STAMP(cta + 256, 5);
+        if (builder && !*s_abort) {
+            float xv[8];
+            pipe_load_x8<DT>(p.x, kbase + koff, xvec, xv);
             float lo[8], hi[4];
 #pragma unroll
             for (int e = 0; e < 8; ++e)
@@ -223,46 +299,19 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
 #pragma unroll
                 for (int l = 0; l < 8; ++l) tbl[(qe * 32 + h * 8 + l) * 64 + slot] = th + lo[l];
             }
+            // sum of the 32 activations of a k-row (for the q_bias term): four byte slots side by side
+            float rs = ((xv[0] + xv[1]) + (xv[2] + xv[3])) + ((xv[4] + xv[5]) + (xv[6] + xv[7]));
+            rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+            rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+            if (qe == 0 && (lane & 3) == 0) rowsum[krow_b] = rs;
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(kPipeGroups * 256) : "memory");
-        if (tid < 16) {
-            const uint32_t base = (tid >> 3) * 32 + (tid & 7) * 4;
-            rowsum[tid] = tbl[255 * 64 + base] + tbl[255 * 64 + base + 1] + tbl[255 * 64 + base + 2] + tbl[255 * 64 + base + 3];
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(kPipeGroups * 256) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(NCONS) : "memory");
         DD_STAMP(cta + 256, 1);
-
-        // two groups of 8 warps take alternate stages.  Inside a group:
-        // warp = (k half, 32-output block); lane = (k-row j, c).  Row j reads the 16-byte groups
-        // tA = (j + c) & 7 and tB = tA ^ 4 of the block's 128-byte line segment.
-        const uint32_t j = lane & 7, c = lane >> 3;
-        const uint32_t grp = warp >> 3;
-        const uint32_t blk = warp & 3, khalf = (warp >> 2) & 1;
-        const uint32_t krow = khalf * 8 + j;
-        const uint32_t tA = (j + c) & 7, tB = tA ^ 4;
-        uint32_t sel[4], lb[4];
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-            const uint32_t byte = (s + c) & 3;
-            sel[s] = 0x6504u | (byte << 4);                // result bytes = {lb.b0, word.byte[byte], lb.b1, lb.b2}
-            // b0 = slot offset inside a 256-byte entry row, b1 = bits 16..23 of the tables' window address
-            lb[s] = (khalf * 128 + (4 * j + byte) * 4) | (((smem_u32(tbl) >> 16) & 0xffu) << 8);
-        }
         const float sx = rowsum[krow];
-        const uint32_t g = (32 * krow) / p.group;          // scale group of this lane's k-row inside the slice
-        const uint32_t nA = blk * 32 + 4 * tA, nB = blk * 32 + 4 * tB;
-        // partner lanes of the reduction over k-rows (lanes sharing (j + c) & 3 hold the same two groups)
-        const uint32_t p4 = lane ^ 4, p2 = lane ^ 18;
-        const uint32_t p1 = (j ^ 1) + 8 * (((j & 1) ? c + 1 : c + 3) & 3);
-        const bool swapAB = (tA & 4) != 0;                  // after the swap X = group r, Y = group r + 4, r = tA & 3
-        const uint32_t r = tA & 3;
-        const uint32_t n_out = blk * 32 + ((j & 4) ? 16 : 0) + 4 * r + (j & 3);
 
-        for (uint32_t i = grp; i < nst; i += kPipeGroups) {
+        for (uint32_t i = grp; i < nst && !*s_abort; i += kPipeGroups) {
             const uint32_t s = i % S;
-#if !(defined(DD_EXP) && DD_EXP == 2)
-            if (!mbar_wait(bar_full + 8 * s, (i / S) & 1u, s_abort)) break;
-#endif
+            if (!mbar_wait(bar_full + 8 * s, (i / S) & 1u, s_abort, geo.wait_ns)) break;
             if (i == 0) DD_STAMP(cta + 256, 2);
             const unsigned char* st = stage_ptr(s);
             const unsigned char* wl = st + krow * (BITS * kPipeLine);
@@ -273,34 +322,8 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
             lds4f<DT>(bl, nB, y8 + 4);
 #pragma unroll
             for (int q = 0; q < 8; ++q) y8[q] *= sx;
-#if defined(DD_EXP) && DD_EXP == 1
-            y8[0] += __uint_as_float(*reinterpret_cast<const uint32_t*>(wl + nA * 4));   // stream only: no lookups
-#else
-#if defined(DD_VAR) && DD_VAR == 3
-#pragma unroll 1
-#else
 #pragma unroll
-#endif
             for (int pl = 0; pl < BITS; ++pl) {
-#if defined(DD_VAR) && DD_VAR == 1
-#pragma unroll 1
-                for (int hh = 0; hh < 2; ++hh) {
-                    const uint4 wv = *reinterpret_cast<const uint4*>(wl + pl * kPipeLine + (hh ? nB : nA) * 4);
-                    float a4[4];
-                    lds4f<DT>(al + pl * (kPipeStageN * ESZ), hh ? nB : nA, a4);
-                    const uint32_t wq[4] = {wv.x, wv.y, wv.z, wv.w};
-                    float v[16];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q)
-#pragma unroll
-                        for (int ss = 0; ss < 4; ++ss) v[q * 4 + ss] = lds_f32(__byte_perm(wq[q], lb[ss], sel[ss]));
-                    float r4[4];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) r4[q] = a4[q] * ((v[q * 4] + v[q * 4 + 1]) + (v[q * 4 + 2] + v[q * 4 + 3]));
-                    if (hh) { y8[4] += r4[0]; y8[5] += r4[1]; y8[6] += r4[2]; y8[7] += r4[3]; }
-                    else { y8[0] += r4[0]; y8[1] += r4[1]; y8[2] += r4[2]; y8[3] += r4[3]; }
-                }
-#else
                 const uint4 wA = *reinterpret_cast<const uint4*>(wl + pl * kPipeLine + nA * 4);
                 const uint4 wB = *reinterpret_cast<const uint4*>(wl + pl * kPipeLine + nB * 4);
                 float a8[8];
@@ -315,13 +338,9 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
 #pragma unroll
                 for (int q = 0; q < 8; ++q)
                     y8[q] = fmaf(a8[q], (v[q * 4] + v[q * 4 + 1]) + (v[q * 4 + 2] + v[q * 4 + 3]), y8[q]);
-#endif
             }
-#endif
             __syncwarp();
-#if !(defined(DD_EXP) && DD_EXP == 2)
             if (lane == 0) mbar_arrive(bar_empty + 8 * s);      // all shared reads of the stage are done
-#endif
             // X = values of group r, Y = values of group r + 4; reduce over the 8 k-row lanes, halving
             float y4[4], y2[2], y1;
 #pragma unroll
@@ -343,17 +362,56 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
                 const float keep = (j & 1) ? y2[1] : y2[0];
                 y1 = keep + __shfl_sync(0xffffffffu, send, p1);
             }
-            atomicAdd(&f.acc[(st0 + i) * kPipeStageN + n_out], y1);
+            atomicAdd(acc_lane + i * kPipeStageN, y1);
         }
     }
-    if (warp == kPipeGroups * 8) pdl_wait();
-    __syncthreads();
     DD_STAMP(cta + 256, 3);
-    if (*s_abort) {
-        if (tid == 0) atomicExch(f.err, 1u);
+    // Whatever happened above, the CTA takes part in the tile's protocol, so that accumulator, counters and tickets
+    // are clean for the next launch; a wait that ran out is reported through the error word.
+    if (!geo.poll) {
+        __syncthreads();
+        if (*s_abort && tid == 0) raise_error(f.err, *s_abort);
+        arrive_and_finalize<DT>(f, tile, tile + 1, s_flag, kPipeThreads);
+        DD_STAMP(cta + 256, 4);
         return;
     }
-    arrive_and_finalize<DT>(f, tile, tile + 1, s_flag, kPipeThreads);
+    __threadfence();            // this thread's additions to the accumulator are performed
+    __syncthreads();
+    if (*s_abort && tid == 0) raise_error(f.err, *s_abort);
+    if (ks + 1 != p.n_kslices) {
+        // result unused: a fire-and-forget increment; the upper half tells the finalizer that a CTA gave up
+        if (tid == 0) atomicAdd(&f.tickets[tile], *s_abort ? 0x10001u : 1u);
+        DD_STAMP(cta + 256, 4);
+        return;
+    }
+    // finalizer of the tile: the other K slices' CTAs have lower block indices, so they were dispatched before
+    // this one; wait (bounded) until all of them have published
+    if (tid == 0) {
+        const unsigned want = p.n_kslices - 1u;
+        unsigned v = want ? ld_acquire_u32(&f.tickets[tile]) : 0u;
+        if ((v & 0xffffu) != want) {
+            const long long t0 = clock64();
+            const long long limit = 2ll * (long long)geo.wait_ns;
+            do {
+                v = ld_acquire_u32(&f.tickets[tile]);
+            } while ((v & 0xffffu) != want && clock64() - t0 <= limit);
+        }
+        // 0: a peer never arrived (the workspace stays dirty until decdec_stream_reset); 1: fold; 2: somebody gave up, clear only
+        unsigned how = ((v & 0xffffu) != want) ? 0u : ((v >> 16) || *s_abort) ? 2u : 1u;
+        if (how == 0u) raise_error(f.err, 3u);
+        *s_flag = how;
+    }
+    __syncthreads();
+    const unsigned how = *s_flag;
+    const uint32_t n0 = st0 * kPipeStageN, n1 = min(p.N, n0 + nst * kPipeStageN);
+    if (how == 1u) {
+        __threadfence();
+        finalize_span<DT>(f, n0, n1, kPipeThreads);
+    } else if (how == 2u) {
+        // an unfinished launch leaves y alone; the accumulator is cleaned for the next one
+        for (uint32_t n = n0 + 4u * tid; n < n1; n += 4u * kPipeThreads) __stcg(reinterpret_cast<float4*>(f.acc + n), make_float4(0.f, 0.f, 0.f, 0.f));
+    }
+    if (how && tid == 0) f.tickets[tile] = 0u;
     DD_STAMP(cta + 256, 4);
 }
 

@@ -12,6 +12,20 @@
 #include <mutex>
 #include <utility>
 
+namespace dd {
+uint32_t device_sms() {
+    static uint32_t sms[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!sms[dev]) {
+        int n = 0;
+        sms[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? (uint32_t)n : 148u;
+    }
+    return sms[dev];
+}
+
+}  // namespace dd
+
 namespace {
 
 using namespace dd;
@@ -38,8 +52,9 @@ constexpr uint32_t kTicketCap = 1u << 13;
 struct Workspace {
     float* acc = nullptr;
     unsigned* tickets = nullptr;
-    unsigned* err = nullptr;     // last word of the ticket allocation
-    float* acc2 = nullptr;       // second half of the accumulator allocation (compensation sums)
+    unsigned* err = nullptr;          // device-visible address of the error word (mapped pinned host memory)
+    volatile unsigned* err_host = nullptr;   // the same word as the host sees it: read before every launch, no copy needed
+    float* acc2 = nullptr;            // second half of the accumulator allocation (compensation sums)
 };
 
 std::mutex g_mu;
@@ -47,12 +62,22 @@ std::map<std::pair<int, cudaStream_t>, Workspace> g_ws;
 std::map<int, Workspace> g_ws_first;                       // first workspace of a device: capture fallback
 std::map<int, std::pair<cudaStream_t, std::pair<cudaEvent_t, cudaEvent_t>>> g_side;   // dummy_* side stream
 
+// A launch that gave up on a wait left its code in the workspace's error word: every later call on that stream
+// fails until decdec_stream_reset, instead of computing on top of an unfinished result.
+int check_ws(const Workspace& w) {
+    const unsigned code = w.err_host ? *w.err_host : 0u;
+    if (code)
+        return fail(DECDEC_E_DEVICE, "an earlier launch on this stream gave up waiting (device code %u); read it with "
+                                     "decdec_stream_status and clear it with decdec_stream_reset", code);
+    return 0;
+}
+
 int get_workspace(cudaStream_t stream, Workspace* out) {
     int dev = 0;
     DD_CUDA(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_ws.find({dev, stream});
-    if (it != g_ws.end()) { *out = it->second; return 0; }
+    if (it != g_ws.end()) { *out = it->second; return check_ws(*out); }
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
     DD_CUDA(cudaStreamIsCapturing(stream, &cs));
     if (cs != cudaStreamCaptureStatusNone) {
@@ -63,7 +88,7 @@ int get_workspace(cudaStream_t stream, Workspace* out) {
         if (f == g_ws_first.end())
             return fail(DECDEC_E_INVALID, "first call on a device must happen outside stream capture (workspace allocation)");
         *out = f->second;
-        return 0;
+        return check_ws(*out);
     }
     Workspace w;
     if (cudaMalloc(&w.acc, 2 * kAccCap * sizeof(float)) != cudaSuccess) return fail(DECDEC_E_NOMEM, "cudaMalloc(accumulator) failed");
@@ -71,7 +96,20 @@ int get_workspace(cudaStream_t stream, Workspace* out) {
     DD_CUDA(cudaMemset(w.acc, 0, 2 * kAccCap * sizeof(float)));
     w.acc2 = w.acc + kAccCap;
     DD_CUDA(cudaMemset(w.tickets, 0, (kTicketCap + 4) * sizeof(unsigned)));
-    w.err = w.tickets + kTicketCap;
+    {
+        // the error word lives in mapped pinned host memory: a kernel that gives up stores into it, and the
+        // host sees it at the next call without a copy or a synchronisation
+        void* h = nullptr;
+        void* d = nullptr;
+        if (cudaHostAlloc(&h, 64, cudaHostAllocMapped) != cudaSuccess || cudaHostGetDevicePointer(&d, h, 0) != cudaSuccess) {
+            cudaGetLastError();
+            cudaFree(w.acc); cudaFree(w.tickets);
+            return fail(DECDEC_E_NOMEM, "cudaHostAlloc(error word) failed");
+        }
+        memset(h, 0, 64);
+        w.err = reinterpret_cast<unsigned*>(d);
+        w.err_host = reinterpret_cast<volatile unsigned*>(h);
+    }
     DD_CUDA(cudaDeviceSynchronize());
     g_ws[{dev, stream}] = w;
     if (!g_ws_first.count(dev)) g_ws_first[dev] = w;
@@ -160,17 +198,6 @@ int fill_dec(const Config* c, const void* x, bool fused_select, uint32_t n_tiles
 // SMs left to the GEMV thread blocks of a fused launch.  A few compensation thread blocks take their SMs
 // out of the GEMV's single wave (the GEMV grid shrinks accordingly); many of them mean the launch is bound
 // by the host link anyway, and the GEMV keeps its full grid and runs in the gaps.
-uint32_t device_sms() {
-    static uint32_t sms[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (!sms[dev]) {
-        int n = 0;
-        sms[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? (uint32_t)n : 148u;
-    }
-    return sms[dev];
-}
-
 uint32_t gemv_sm_budget(const Config* c, bool fused_select) {
     const uint32_t sms = device_sms();
     if (!c) return sms;
@@ -275,12 +302,8 @@ int run_bcq(Config* c, const void* x, void* y, const int32_t* qw, const void* al
     PipeGeom geo;
     const bool pipe = env_u32("DECDEC_BCQ_PIPE", 1) && bcq_pipe_geometry(N, K, g.bits, g.group, dtype, g.n_kslices, &geo, gemv_sm_budget(c, true));
     FinParams f;
-    if (pipe) {
-        tile_units = geo.tile_stages * (kPipeStageN / 32);
-        if (int r = setup_fin(&f, ws, y, N, tile_units, g.n_kslices)) return r;
-    } else {
-        if (int r = setup_fin(&f, ws, y, N, tile_units, g.n_kslices)) return r;
-    }
+    if (pipe) tile_units = geo.tile_stages * (kPipeStageN / 32);
+    if (int r = setup_fin(&f, ws, y, N, tile_units, g.n_kslices)) return r;
     g.n_cta = g.n_kslices * f.n_tiles;
     DecParams d;
     memset(&d, 0, sizeof(d));
@@ -288,6 +311,8 @@ int run_bcq(Config* c, const void* x, void* y, const int32_t* qw, const void* al
         if (int r = fill_dec(c, x, true, f.n_tiles, &d)) return r;
         if (d.n_cta) { f.expected += d.n_rowparts; f.acc2 = ws.acc2; f.scales = d.scales; }
     }
+    // GEMV-only launches let the last K slice's CTA of a tile poll and fold (DECDEC_BCQ_POLL=0: everybody takes a ticket)
+    if (pipe) geo.poll = (d.n_cta == 0 && env_u32("DECDEC_BCQ_POLL", 1)) ? 1u : 0u;
     if (pipe) DD_CUDA(launch_bcq_pipe(dtype, g, d, f, geo, s));
     else DD_CUDA(launch_bcq(dtype, g, d, f, s));
     return 0;
@@ -327,6 +352,7 @@ int run_anyprec(Config* c, const void* x, void* y, const int32_t* qw, uint32_t p
     }
     g.direct = d.n_cta ? 0u : 1u;
     if (pipe) {
+        pgeo.direct = g.direct;
         g.direct = 0u;
         DD_CUDA(launch_anyprec_pipe(dtype, g, d, f, pgeo, s));
         return 0;
@@ -410,6 +436,46 @@ extern "C" {
 const char* decdec_last_error(void) { return g_err; }
 
 int decdec_compiled_arch(void) { return 100; }
+
+int decdec_stream_status(void* stream, uint32_t* error_out) {
+    if (!error_out) return fail(DECDEC_E_INVALID, "null output pointer");
+    int dev = 0;
+    DD_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_ws.find({dev, reinterpret_cast<cudaStream_t>(stream)});
+    *error_out = (it != g_ws.end() && it->second.err_host) ? *it->second.err_host : 0u;
+    return 0;
+}
+
+#ifdef DD_BEACON
+int decdec_debug_beacon(void* stream, uint32_t* out16) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto it = g_ws.find({dev, reinterpret_cast<cudaStream_t>(stream)});
+    if (it == g_ws.end()) return -1;
+    for (int i = 0; i < 16; ++i) out16[i] = it->second.err_host[i];
+    return 0;
+}
+#endif
+
+int decdec_stream_reset(void* stream) {
+    int dev = 0;
+    DD_CUDA(cudaGetDevice(&dev));
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    Workspace w;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        auto it = g_ws.find({dev, s});
+        if (it == g_ws.end()) return 0;
+        w = it->second;
+    }
+    DD_CUDA(cudaStreamSynchronize(s));
+    DD_CUDA(cudaMemsetAsync(w.acc, 0, 2 * kAccCap * sizeof(float), s));
+    DD_CUDA(cudaMemsetAsync(w.tickets, 0, (kTicketCap + 4) * sizeof(unsigned), s));
+    DD_CUDA(cudaStreamSynchronize(s));
+    if (w.err_host) *w.err_host = 0u;
+    return 0;
+}
 
 int decdec_create_context(uint32_t num_tb, int32_t* rows, void* acts, uint32_t buffer_size, int dtype, uintptr_t* out) {
     if (!out) return fail(DECDEC_E_INVALID, "null output handle");

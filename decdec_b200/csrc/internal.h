@@ -13,7 +13,7 @@ namespace dd {
 cudaError_t launch_dec_only(int dt, const DecParams& d, const FinParams& f, cudaStream_t s);
 cudaError_t launch_bcq(int dt, const BcqParams& g, const DecParams& d, const FinParams& f, cudaStream_t s);
 bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, int dt, uint32_t n_kslices, PipeGeom* geo,
-                       uint32_t sm_budget = 148);   // SMs the GEMV thread blocks may fill in one wave
+                       uint32_t sm_budget);   // SMs the GEMV thread blocks may fill in one wave
 cudaError_t launch_bcq_pipe(int dt, const BcqParams& g, const DecParams& d, const FinParams& f, const PipeGeom& geo, cudaStream_t s);
 cudaError_t launch_anyprec(int dt, const ApParams& g, const DecParams& d, const FinParams& f, cudaStream_t s);
 bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* geo, uint32_t sm_budget = 148);
@@ -26,6 +26,7 @@ cudaError_t launch_bcq_dequant(int dt, const uint32_t* qweight, const void* alph
 cudaError_t launch_burner(int blocks, long long iters, cudaStream_t s);
 
 int set_last_error(int code, const char* msg);
+uint32_t device_sms();
 size_t dec_only_smem();
 size_t anyprec_smem(uint32_t K, bool fast3);
 size_t sqllm_smem(uint32_t K);

@@ -62,17 +62,24 @@ bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* ge
     geo->rows_per_stage = R;
     geo->x_bytes = (K * 2 + 127u) & ~127u;
     geo->stage_bytes = (R * (3 * rowbytes + 16) + 127u) & ~127u;
-    const uint32_t budget = 227 * 1024 - kApPipeHdr - geo->x_bytes;
-    uint32_t smax = budget / geo->stage_bytes;
-    if (smax > 8) smax = 8;
-    if (smax < 2) return false;
     if (sm_budget == 0) sm_budget = 1;
     uint32_t rows = (N + sm_budget - 1) / sm_budget;
     rows = ((rows + 31) / 32) * 32;
     geo->rows_per_cta = rows;
+    geo->part_bytes = (rows * 4u + 127u) & ~127u;
+    if (kApPipeHdr + geo->x_bytes + geo->part_bytes + 2u * geo->stage_bytes > 227u * 1024u) return false;
+    const uint32_t budget = 227 * 1024 - kApPipeHdr - geo->x_bytes - geo->part_bytes;
+    uint32_t smax = budget / geo->stage_bytes;
+    if (smax > 8) smax = 8;
+    if (smax < 2) return false;
     const uint32_t nst = rows / R;
     geo->stages = nst < smax ? nst : smax;
-    geo->smem_bytes = kApPipeHdr + geo->x_bytes + geo->stages * geo->stage_bytes;
+    geo->smem_bytes = kApPipeHdr + geo->x_bytes + geo->part_bytes + geo->stages * geo->stage_bytes;
+    geo->direct = 0;        // set by the caller
+    {
+        const char* w = getenv("DECDEC_PIPE_WAIT_NS");
+        geo->wait_ns = (w && *w) ? (uint32_t)strtoul(w, nullptr, 10) : 50u * 1000u * 1000u;
+    }
     if (geo->smem_bytes < (uint32_t)DecSmem::kBytes) geo->smem_bytes = DecSmem::kBytes;
     return true;
 }

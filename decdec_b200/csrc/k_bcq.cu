@@ -48,13 +48,13 @@ static int pdl_mode() {
 template <int DT, int BITS>
 static cudaError_t go_pipe(const BcqParams& g, const DecParams& d, const FinParams& f, const PipeGeom& geo, const PipeMaps& maps,
                            cudaStream_t s) {
-    static size_t configured[64] = {};
+    static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 64 && configured[dev] < geo.smem_bytes) {
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(k_bcq_pipe<DT, BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
-        configured[dev] = 227 * 1024;
+        configured[dev] = true;
     }
     // programmatic dependent launch: CTAs may become resident (and prefetch weights) while the previous
     // kernel of the stream drains; the kernel waits for it before touching activations or outputs
@@ -123,11 +123,23 @@ cudaError_t launch_bcq_pipe(int dt, const BcqParams& g, const DecParams& d, cons
     }
 }
 
+static uint32_t env_u32_k(const char* name, uint32_t dflt) {
+    const char* v = getenv(name);
+    return (v && *v) ? (uint32_t)strtoul(v, nullptr, 10) : dflt;
+}
+
 // Stage geometry of the pipelined kernel; returns false if the shape is not eligible.
+// sm_budget = SMs the GEMV CTAs may fill in one wave.
 bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, int dt, uint32_t n_kslices, PipeGeom* geo,
                        uint32_t sm_budget) {
     if (N % kPipeStageN || K % kBcqSlice || bits < 2 || bits > 4) return false;
     if (group < 32 || group > (uint32_t)kBcqSlice || kBcqSlice % group) return false;
+    // the table block sits at the first 64 KB multiple of the shared window; dynamic shared memory starts right
+    // after the bytes the system reserves per CTA (this kernel has no static shared memory)
+    int dev = 0, reserved = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev) != cudaSuccess) { cudaGetLastError(); return false; }
+    if ((uint32_t)reserved != 65536u - kPipeTblOffAssumed) return false;
     const uint32_t esz = dt == FP32 ? 4 : 2;
     const uint32_t groups = kBcqSlice / group;
     geo->w_bytes = 16 * bits * kPipeLine;
@@ -140,13 +152,16 @@ bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, in
     if (smax > 8) smax = 8;
     if (smax < 2) return false;
     const uint32_t nst_total = N / kPipeStageN;
-    // one CTA (16 consumer warps) per SM; tiles sized so that the grid is at most one wave
+    // one CTA per SM; tiles sized so that the grid is at most one wave
     uint32_t per1 = sm_budget / n_kslices; if (per1 == 0) per1 = 1;
     geo->tile_stages = (nst_total + per1 - 1) / per1;
     geo->stages = geo->tile_stages < smax ? geo->tile_stages : smax;
     const uint32_t after = geo->stages > n_before ? geo->stages - n_before : 0;
     geo->smem_bytes = kPipeTblOffAssumed + kBcqTableBytes + after * geo->stage_bytes;
     if (geo->smem_bytes < (uint32_t)DecSmem::kBytes) geo->smem_bytes = DecSmem::kBytes;
+    geo->poll = 0;                  // set by the caller
+    geo->wait_ns = env_u32_k("DECDEC_PIPE_WAIT_NS", 50u * 1000u * 1000u);
+    geo->test_skip_last = env_u32_k("DECDEC_TEST_WITHHOLD_STAGE", 0) ? 1u : 0u;
     return true;
 }
 

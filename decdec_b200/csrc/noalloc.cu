@@ -88,7 +88,7 @@ extern "C" int decdec_lutgemm_gemv_noalloc(const void* x, void* y, const int32_t
     g.K = K; g.N = N; g.bits = (uint32_t)bits; g.group = (uint32_t)group;
     g.n_kslices = cdiv(K, kBcqSlice);
     PipeGeom geo;
-    const bool pipe = bcq_pipe_geometry(N, K, g.bits, g.group, dtype, g.n_kslices, &geo);
+    const bool pipe = bcq_pipe_geometry(N, K, g.bits, g.group, dtype, g.n_kslices, &geo, device_sms());
     uint32_t tile_units;
     if (pipe) {
         tile_units = geo.tile_stages * (kPipeStageN / 32);
@@ -109,7 +109,7 @@ extern "C" int decdec_lutgemm_gemv_noalloc(const void* x, void* y, const int32_t
     f.n_tiles = cdiv(cdiv(N, 32), tile_units);
     f.expected = g.n_kslices;
     if (f.n_tiles > kMaxTiles) return set_last_error(DECDEC_E_UNSUPPORTED, "too many output tiles for the static scratch");
-    g.n_cta = g.n_kslices * f.n_tiles;
+    g.n_cta = f.expected * f.n_tiles;
     DecParams d = {};
 
     // the array keeps whatever the last call left: clear what this call needs to start at zero

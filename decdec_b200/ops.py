@@ -310,3 +310,19 @@ __all__ = [
     "dec", "unfused_dec", "anyprec_dequant", "anyprec_gemv", "lutgemm_gemv", "sqllm_gemv",
     "dec_anyprec", "dec_lutgemm", "dec_sqllm", "dummy_anyprec", "dummy_lutgemm", "dummy_sqllm",
 ]
+
+
+# ---- additions without a counterpart in the reference binding -------------------------------------------
+
+def stream_status() -> int:
+    """Error word of the current stream's workspace (0 = fine; 1 = a bounded wait inside a kernel ran out,
+    2 = a launch did not get the shared-memory layout it was sized for).  Does not synchronise."""
+    err = C.c_uint32(0)
+    _call("decdec_stream_status", _stream(), C.byref(err))
+    return int(err.value)
+
+
+def stream_reset() -> None:
+    """Waits for the current stream, clears its error word and its accumulator workspace."""
+    _call("decdec_stream_reset", _stream())
+

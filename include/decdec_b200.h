@@ -35,7 +35,8 @@ enum {
     DECDEC_E_INVALID = -1,      /* bad argument (shape, dtype, alignment, null pointer) */
     DECDEC_E_UNSUPPORTED = -2,  /* valid in the reference but not implemented here */
     DECDEC_E_CUDA = -3,         /* a CUDA runtime call failed */
-    DECDEC_E_NOMEM = -4         /* allocation failed */
+    DECDEC_E_NOMEM = -4,        /* allocation failed */
+    DECDEC_E_DEVICE = -5        /* an earlier launch on the stream gave up on a bounded wait (see decdec_stream_status) */
 };
 
 /* Launch geometry of a config; replaces the dict of read_dec_config (dec_config.cu:337-354). */
@@ -55,6 +56,17 @@ const char* decdec_last_error(void);
 
 /* Version / build probe: returns the compute capability the kernels were compiled for (100). */
 int decdec_compiled_arch(void);
+
+/* ---- device-side failures.  NO COUNTERPART IN THE REFERENCE (it ignores launch and device errors,
+ * dec_config.cu:204-208).  Every wait inside the kernels of this library is bounded; a thread block that gives up
+ * stores a code into the error word of the (device, stream) workspace: 1 = a wait for a shared-memory stage ran
+ * out (DECDEC_PIPE_WAIT_NS, default 50 ms), 2 = the launch did not get the shared-memory layout it was sized for.
+ * The output of that launch is then incomplete.  The word lives in mapped host memory, so every later compute call
+ * on that stream sees it without a copy and fails with DECDEC_E_DEVICE until the stream is reset.
+ *   decdec_stream_status  *error_out = the word (0 = fine); does not synchronise.
+ *   decdec_stream_reset   waits for the stream, clears the word and the accumulator workspace. */
+int decdec_stream_status(void* stream, uint32_t* error_out);
+int decdec_stream_reset(void* stream);
 
 /* ---- context (reference: create_dec_context, dec_context.cu:62-103) ------------------------------
  * num_tb: thread blocks given to the compensation role.  selected_rows_dev / selected_acts_dev:

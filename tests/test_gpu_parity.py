@@ -624,3 +624,36 @@ def test_residual_on_device_and_graph_capture(ops):
         exp_rows, exp_acts, _ = P.expected_selection(x, thr, 16, "fp16")
         delta = ofw.dec_delta(P.to_np(x), exp_rows, cs.numpy(), P.to_np(rs), exp_acts)
         _assert_close(y, ofw.layer_output(L["w_hat"], P.to_np(x), None, delta), "fp16", "graph replay")
+
+
+def test_wait_that_runs_out_is_reported_and_recoverable(ops):
+    """Device-side failure handling without a GPU fault: under a test-only launch flag the producer of the pipelined
+    binary-coded GEMV never issues its last stage (nothing is in flight for it), so the consumers' wait for that stage,
+    given a 2 ms limit, runs out.  The launch must return, leave y untouched, raise the stream's error word, make the
+    next call fail loudly, and after a reset the stream must compute correctly again."""
+    N, K = 1024, 2048
+    L = P.random_bcq_layer(N, K, 3, 128, seed=77)
+    x = P.make_activation(K, seed=78)
+    y0 = _y0(N, "fp16")
+    y = y0.clone().cuda()
+    qw, al, qb, xd = L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda(), x.cuda()
+    ops.lutgemm_gemv(xd, torch.zeros_like(y), qw, al, qb, 3, 128)      # workspace exists, kernel configured
+    torch.cuda.synchronize()
+    assert ops.stream_status() == 0
+    os.environ["DECDEC_TEST_WITHHOLD_STAGE"] = "1"
+    os.environ["DECDEC_PIPE_WAIT_NS"] = "2000000"
+    try:
+        ops.lutgemm_gemv(xd, y, qw, al, qb, 3, 128)
+        torch.cuda.synchronize()
+    finally:
+        del os.environ["DECDEC_TEST_WITHHOLD_STAGE"]
+        del os.environ["DECDEC_PIPE_WAIT_NS"]
+    assert ops.stream_status() == 1, "the wait that ran out was not reported"
+    assert torch.equal(y.cpu(), y0), "an unfinished launch must not touch the output"
+    with pytest.raises(RuntimeError, match="gave up waiting"):
+        ops.lutgemm_gemv(xd, y, qw, al, qb, 3, 128)
+    ops.stream_reset()
+    assert ops.stream_status() == 0
+    ops.lutgemm_gemv(xd, y, qw, al, qb, 3, 128)
+    torch.cuda.synchronize()
+    _assert_close(y, ofw.layer_output(L["w_hat"], P.to_np(x), P.to_np(y0)), "fp16", "call after reset")

@@ -15,13 +15,16 @@
 // (K slice, output tile) and the CTAs of a tile are neighbours in the grid.  After every stage a lane adds its
 // 32-channel-row total into the fp32 accumulator of the workspace (red.global, fire and forget).  How a tile is
 // finished depends on the launch:
-//  * GEMV-only launches: the CTA of the LAST K slice of a tile is its finalizer.  The others publish their sums
-//    (fence, one release increment of the tile's counter) and leave; the finalizer, which the hardware dispatched
-//    after them, polls the counter (bounded) and folds the accumulator into y.  Nobody pays an atomic round trip.
+//  * GEMV-only launches: the accumulator holds one 64-bit word per output = {fixed-point sum (48 bits, 2^-20),
+//    arrivals that were not finite (8 bits), arrivals (8 bits; two per CTA, one per k half)}.  A lane adds its partial sum and one arrival with
+//    ONE atomic; the lane whose atomic returns the last arrival count holds the complete sum, writes y (single
+//    rounding) and clears the word.  No fence, no ticket, no second pass over the accumulator; integer addition
+//    also makes the result independent of the arrival order.  The atomic's result is only looked at after the
+//    next stage has been computed, so its round trip is hidden except for the last stage.
 //  * fused launches (compensation CTAs in the same grid, which finish late): every CTA takes a ticket and the last
 //    arriver folds (common.cuh), so no CTA spins while the host link is busy.
-// Thread-block clusters with a reduction through distributed shared memory were built and measured for this split
-// and lost: only 15 clusters of 8 CTAs with this shared-memory footprint are resident at once (120 of 148 SMs),
+// Measured dead ends for this split: a designated finalizer per tile that polls a counter (no faster than tickets),
+// and thread-block clusters with a reduction through distributed shared memory: only 15 clusters of 8 CTAs with this shared-memory footprint are resident at once (120 of 148 SMs),
 // cluster placement delays the early start that programmatic dependent launch gives, and walking several K slices
 // per CTA costs about 1.5 us per table rebuild.
 //
@@ -51,7 +54,7 @@ struct PipeGeom {
     uint32_t a_bytes;        // alpha part of a stage
     uint32_t tile_stages;    // stages (128 outputs each) per output tile
     uint32_t smem_bytes;     // dynamic shared memory of the launch
-    uint32_t poll;           // 1: GEMV-only launch, the CTA of the last K slice polls the tile's counter and folds
+    uint32_t packed;         // 1: GEMV-only launch, sums and arrival counts travel in one 64-bit atomic per output
     uint32_t wait_ns;        // limit of one bounded wait (DECDEC_PIPE_WAIT_NS)
     uint32_t test_skip_last; // test hook: the producer withholds its last stage, so that a wait runs out
 };
@@ -160,11 +163,26 @@ __device__ __forceinline__ void pipe_load_x8(const void* xbase, uint32_t k0, boo
     }
 }
 
-// acquire load of a tile counter
-__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+// Packed accumulator word of a GEMV-only launch: bits 0..7 arrivals, 8..15 arrivals whose partial sum was not
+// finite, 16..63 the sum as signed fixed point with 20 fractional bits (finite partial sums are clamped to +-2^22).
+__device__ __forceinline__ unsigned long long pack_partial(float v) {
+    const bool finite = fabsf(v) <= 3.0e38f;      // false for inf and NaN
+    const float c = fminf(fmaxf(finite ? v : 0.0f, -4194304.0f), 4194304.0f);
+    const long long q = __float2ll_rn(c * 1048576.0f);
+    return ((unsigned long long)q << 16) + (finite ? 1ull : 0x101ull);
+}
+
+// The atomic of output n returned `old` when `mine` was added: if that was the last of `expected` arrivals, the
+// complete sum goes into y (y0 = the output's value read earlier) and the word is cleared for the next launch.
+template <int DT>
+__device__ __forceinline__ void finish_packed(unsigned long long old, unsigned long long mine, unsigned expected,
+                                              unsigned long long* word, typename Tr<DT>::T* yp, float y0) {
+    const unsigned long long now = old + mine;
+    if ((unsigned)(now & 0xffull) != expected) return;
+    const float sum = (float)((double)((long long)now >> 16) * (1.0 / 1048576.0));
+    const float out = ((now >> 8) & 0xffull) ? __int_as_float(0x7fc00000) : y0 + sum;
+    *yp = Tr<DT>::from_f(out);
+    __stcg(word, 0ull);
 }
 
 template <int DT, int BITS>
@@ -280,6 +298,11 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
         const uint32_t r4 = tA & 3;
         const uint32_t n_out = blk * 32 + ((j & 4) ? 16 : 0) + 4 * r4 + (j & 3);
         float* acc_lane = f.acc + (size_t)st0 * kPipeStageN + n_out;
+        bool pending = false;
+        unsigned long long p_old = 0, p_mine = 0;
+        unsigned long long* p_word = nullptr;
+        T* p_y = nullptr;
+        float p_y0 = 0.0f;
 
         pdl_wait();     // weights are already streaming (producer warp); activations come from earlier kernels
         DD_STAMP(cta + 256, 5);
@@ -362,56 +385,36 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
                 const float keep = (j & 1) ? y2[1] : y2[0];
                 y1 = keep + __shfl_sync(0xffffffffu, send, p1);
             }
-            atomicAdd(acc_lane + i * kPipeStageN, y1);
+            if (!geo.packed) {
+                atomicAdd(acc_lane + i * kPipeStageN, y1);
+            } else {
+                // the previous stage's atomic has long returned: settle it, then send this stage's
+                if (pending) finish_packed<DT>(p_old, p_mine, 2u * p.n_kslices, p_word, p_y, p_y0);
+                const uint32_t n = (st0 + i) * kPipeStageN + n_out;
+                p_word = reinterpret_cast<unsigned long long*>(f.acc) + n;
+                p_y = reinterpret_cast<T*>(f.y) + n;
+                p_y0 = Tr<DT>::to_f(*p_y);
+                p_mine = pack_partial(y1);
+                p_old = atomicAdd(p_word, p_mine);
+                pending = true;
+            }
         }
+        if (pending) finish_packed<DT>(p_old, p_mine, 2u * p.n_kslices, p_word, p_y, p_y0);
     }
     DD_STAMP(cta + 256, 3);
-    // Whatever happened above, the CTA takes part in the tile's protocol, so that accumulator, counters and tickets
-    // are clean for the next launch; a wait that ran out is reported through the error word.
-    if (!geo.poll) {
+    if (geo.packed) {
+        // nothing to hand over: every output was settled by the lane that made its last arrival.  A wait that ran out
+        // leaves the words of the unfinished outputs dirty (their y untouched) until decdec_stream_reset.
         __syncthreads();
         if (*s_abort && tid == 0) raise_error(f.err, *s_abort);
-        arrive_and_finalize<DT>(f, tile, tile + 1, s_flag, kPipeThreads);
         DD_STAMP(cta + 256, 4);
         return;
     }
-    __threadfence();            // this thread's additions to the accumulator are performed
+    // Fused launch: whatever happened above, the CTA takes a ticket on its tile, so that accumulator and tickets are
+    // clean for the next launch; a wait that ran out is reported through the error word.
     __syncthreads();
     if (*s_abort && tid == 0) raise_error(f.err, *s_abort);
-    if (ks + 1 != p.n_kslices) {
-        // result unused: a fire-and-forget increment; the upper half tells the finalizer that a CTA gave up
-        if (tid == 0) atomicAdd(&f.tickets[tile], *s_abort ? 0x10001u : 1u);
-        DD_STAMP(cta + 256, 4);
-        return;
-    }
-    // finalizer of the tile: the other K slices' CTAs have lower block indices, so they were dispatched before
-    // this one; wait (bounded) until all of them have published
-    if (tid == 0) {
-        const unsigned want = p.n_kslices - 1u;
-        unsigned v = want ? ld_acquire_u32(&f.tickets[tile]) : 0u;
-        if ((v & 0xffffu) != want) {
-            const long long t0 = clock64();
-            const long long limit = 2ll * (long long)geo.wait_ns;
-            do {
-                v = ld_acquire_u32(&f.tickets[tile]);
-            } while ((v & 0xffffu) != want && clock64() - t0 <= limit);
-        }
-        // 0: a peer never arrived (the workspace stays dirty until decdec_stream_reset); 1: fold; 2: somebody gave up, clear only
-        unsigned how = ((v & 0xffffu) != want) ? 0u : ((v >> 16) || *s_abort) ? 2u : 1u;
-        if (how == 0u) raise_error(f.err, 3u);
-        *s_flag = how;
-    }
-    __syncthreads();
-    const unsigned how = *s_flag;
-    const uint32_t n0 = st0 * kPipeStageN, n1 = min(p.N, n0 + nst * kPipeStageN);
-    if (how == 1u) {
-        __threadfence();
-        finalize_span<DT>(f, n0, n1, kPipeThreads);
-    } else if (how == 2u) {
-        // an unfinished launch leaves y alone; the accumulator is cleaned for the next one
-        for (uint32_t n = n0 + 4u * tid; n < n1; n += 4u * kPipeThreads) __stcg(reinterpret_cast<float4*>(f.acc + n), make_float4(0.f, 0.f, 0.f, 0.f));
-    }
-    if (how && tid == 0) f.tickets[tile] = 0u;
+    arrive_and_finalize<DT>(f, tile, tile + 1, s_flag, kPipeThreads);
     DD_STAMP(cta + 256, 4);
 }
 

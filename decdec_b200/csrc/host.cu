@@ -311,8 +311,9 @@ int run_bcq(Config* c, const void* x, void* y, const int32_t* qw, const void* al
         if (int r = fill_dec(c, x, true, f.n_tiles, &d)) return r;
         if (d.n_cta) { f.expected += d.n_rowparts; f.acc2 = ws.acc2; f.scales = d.scales; }
     }
-    // GEMV-only launches let the last K slice's CTA of a tile poll and fold (DECDEC_BCQ_POLL=0: everybody takes a ticket)
-    if (pipe) geo.poll = (d.n_cta == 0 && env_u32("DECDEC_BCQ_POLL", 1)) ? 1u : 0u;
+    // GEMV-only launches carry sums and arrival counts in one 64-bit atomic per output (the accumulator allocation
+    // holds kAccCap such words); DECDEC_BCQ_PACKED=0 keeps the ticket protocol
+    if (pipe) geo.packed = (d.n_cta == 0 && g.n_kslices <= 127u && env_u32("DECDEC_BCQ_PACKED", 1)) ? 1u : 0u;
     if (pipe) DD_CUDA(launch_bcq_pipe(dtype, g, d, f, geo, s));
     else DD_CUDA(launch_bcq(dtype, g, d, f, s));
     return 0;

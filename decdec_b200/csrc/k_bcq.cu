@@ -159,7 +159,7 @@ bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, in
     const uint32_t after = geo->stages > n_before ? geo->stages - n_before : 0;
     geo->smem_bytes = kPipeTblOffAssumed + kBcqTableBytes + after * geo->stage_bytes;
     if (geo->smem_bytes < (uint32_t)DecSmem::kBytes) geo->smem_bytes = DecSmem::kBytes;
-    geo->poll = 0;                  // set by the caller
+    geo->packed = 0;                // set by the caller
     geo->wait_ns = env_u32_k("DECDEC_PIPE_WAIT_NS", 50u * 1000u * 1000u);
     geo->test_skip_last = env_u32_k("DECDEC_TEST_WITHHOLD_STAGE", 0) ? 1u : 0u;
     return true;

@@ -107,6 +107,28 @@ __device__ __forceinline__ float lds_f32(uint32_t saddr) {
     return v;
 }
 
+// Packed accumulator word (launches without tickets): bits 0..7 arrivals, 8..15 arrivals whose partial sum was not
+// finite, 16..63 the sum as signed fixed point with 20 fractional bits (finite partial sums are clamped to +-2^22).
+__device__ __forceinline__ unsigned long long pack_partial(float v) {
+    const bool finite = fabsf(v) <= 3.0e38f;      // false for inf and NaN
+    const float c = fminf(fmaxf(finite ? v : 0.0f, -4194304.0f), 4194304.0f);
+    const long long q = __float2ll_rn(c * 1048576.0f);
+    return ((unsigned long long)q << 16) + (finite ? 1ull : 0x101ull);
+}
+
+// The atomic of output n returned `old` when `mine` was added: if that was the last of `expected` arrivals, the
+// complete sum goes into y (y0 = the output's value read earlier) and the word is cleared for the next launch.
+template <int DT>
+__device__ __forceinline__ void finish_packed(unsigned long long old, unsigned long long mine, unsigned expected,
+                                              unsigned long long* word, typename Tr<DT>::T* yp, float y0) {
+    const unsigned long long now = old + mine;
+    if ((unsigned)(now & 0xffull) != expected) return;
+    const float sum = __ll2float_rn((long long)now >> 16) * (1.0f / 1048576.0f);
+    const float out = ((now >> 8) & 0xffull) ? __int_as_float(0x7fc00000) : y0 + sum;
+    *yp = Tr<DT>::from_f(out);
+    __stcg(word, 0ull);
+}
+
 // Fold accumulator entries [n0, n1) into y (single rounding) and re-zero them.  n0 is a multiple of 32.
 // Four outputs per thread with all loads issued before the first use: the finalizing CTA sits at the
 // very end of a launch, so its dependent-load round trips are not hidden by anything.

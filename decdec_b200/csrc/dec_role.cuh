@@ -434,4 +434,137 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
     DD_STAMP(cta, 3);
 }
 
+// ---- compensation role of launches without tickets (packed accumulator words, common.cuh) -------------------------
+// The CTA keeps its sums to itself until the end: every thread adds what it fetched into PRIVATE fp32 cells in shared
+// memory (cell (i, slot) at i * stride + slot with an ODD stride: neighbouring lanes hit neighbouring banks both when
+// lanes are slots, in the fetch, and when lanes are the 32 elements i of a vector, in the last pass), over all chunks
+// of the CTA's row part; then one barrier, one pass that adds the row groups of an output, scales it, and makes ONE arrival per
+// output with a 64-bit atomic.  The thread whose atomic returns the last arrival count writes y.  No global partial
+// sums, no fence, no ticket; the residual scales are loaded before the wait for the previous kernel.
+// Needs N % 32 == 0 and fused selection.  Shared memory: DecSmem followed by 32 * (nslots | 1) floats.
+constexpr int kDecPrivOff = (DecSmem::kBytes + 127) & ~127;
+
+// slots a CTA needs for a column range of `nvec` 16-byte vectors when `nthr` threads take part
+__host__ __device__ inline uint32_t dec_private_slots(uint32_t nvec, uint32_t nthr) {
+    const uint32_t R = nvec ? nthr / nvec : 0u;
+    return R ? nvec * R : nvec;
+}
+
+template <int DT>
+__device__ void dec_fetch_private(const DecParams& p, float* cells, uint32_t nslots, uint32_t stride, uint32_t nrows, uint32_t w0,
+                                  uint32_t nvec, const unsigned char* sm, uint32_t nthr) {
+    const int* srow = reinterpret_cast<const int*>(sm + DecSmem::kRow);
+    const float* sact = reinterpret_cast<const float*>(sm + DecSmem::kAct);
+    const uint32_t wpr = p.N / 8;
+    const uint32_t R = nthr / nvec;                 // row groups side by side; 0: fewer threads than vectors
+    const uint32_t Ruse = R ? R : 1u;
+    constexpr int UN = 8;
+    for (uint32_t t = threadIdx.x; t < nslots; t += nthr) {      // one sweep when R >= 1
+        const uint32_t v = R ? t % nvec : t;
+        const uint32_t rg = R ? t / nvec : 0u;
+        const uint32_t col = w0 + 4u * v;
+        float* cell = cells + t;
+        for (uint32_t i0 = rg; i0 < nrows; i0 += Ruse * UN) {
+            uint4 q[UN];
+            float xa[UN];
+#pragma unroll
+            for (int b = 0; b < UN; ++b) {
+                const uint32_t i = i0 + b * Ruse;
+                if (i < nrows) {
+                    q[b] = ldg_stream(reinterpret_cast<const uint4*>(p.cheat + (size_t)srow[i] * wpr + col));
+                    xa[b] = sact[i];
+                } else {
+                    q[b] = make_uint4(0, 0, 0, 0);
+                    xa[b] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float a[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) a[i] = 0.0f;
+#pragma unroll
+                for (int b = 0; b < UN; ++b) {
+                    if (i0 + b * Ruse < nrows) {
+                        dec_decode_word(h ? q[b].z : q[b].x, xa[b], a + 0);
+                        dec_decode_word(h ? q[b].w : q[b].y, xa[b], a + 8);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) cell[(size_t)(16 * h + i) * stride] += a[i];
+            }
+        }
+    }
+}
+
+template <int DT>
+__device__ void dec_role_packed(const DecParams& p, const FinParams& f, uint32_t cta, unsigned char* sm, uint32_t arrivals) {
+    using T = typename Tr<DT>::T;
+    const uint32_t nthr = blockDim.x;
+    const bool first = threadIdx.x < kThreads;
+    pdl_trigger();
+    const uint32_t rp = cta % p.n_rowparts;
+    const uint32_t cp = cta / p.n_rowparts;
+    const uint32_t t0 = (uint32_t)(((uint64_t)cp * f.n_tiles) / p.n_colparts);
+    const uint32_t t1 = (uint32_t)(((uint64_t)(cp + 1) * f.n_tiles) / p.n_colparts);
+    const uint32_t wpr = p.N / 8;
+    const uint32_t w0 = min(wpr, t0 * f.tile_units * 4u);
+    const uint32_t w1 = min(wpr, t1 * f.tile_units * 4u);
+    const uint32_t nvec = (w1 - w0) / 4u;
+    const uint32_t nslots = dec_private_slots(nvec, nthr);
+    const uint32_t stride = nslots | 1u;
+    float* cells = reinterpret_cast<float*>(sm + kDecPrivOff);
+    for (uint32_t i = threadIdx.x; i < 32u * stride; i += nthr) cells[i] = 0.0f;
+    pdl_wait();                             // everything below reads activations / writes shared state
+    DD_STAMP(cta, 0);
+    const uint32_t num_chunks = (p.K + kChunk - 1) / kChunk;
+    for (uint32_t c = rp; c < num_chunks; c += p.n_rowparts) {
+        const uint32_t len = min((uint32_t)kChunk, p.K - c * kChunk);
+        const uint32_t kq = p.k_chunk * len / kChunk;
+        if (kq == 0) continue;
+        if (first) dec_select_chunk<DT>(p, c, kq, cp == 0, sm);
+        __syncthreads();
+        DD_STAMP(cta, 1);
+        if (nvec) dec_fetch_private<DT>(p, cells, nslots, stride, kq, w0, nvec, sm, nthr);
+        __syncthreads();                // the next chunk's selection overwrites srow/sact
+    }
+    __syncthreads();
+    DD_STAMP(cta, 2);
+    // one arrival per output of the column range; lanes take CONSECUTIVE outputs, so the accesses to y, to the
+    // accumulator words and (four lanes per sector) to the scales coalesce
+    const uint32_t R = nthr / max(nvec, 1u);
+    const uint32_t Ruse = R ? R : 1u;
+    T* y = reinterpret_cast<T*>(f.y);
+    const T* sc = reinterpret_cast<const T*>(f.scales);
+    unsigned long long* words = reinterpret_cast<unsigned long long*>(f.acc);
+    const uint32_t nbase = w0 * 8u;
+    // eight outputs per thread and pass: their loads travel together, then their atomics travel together
+    constexpr int U = 8;
+    for (uint32_t ob = threadIdx.x; ob < 32u * nvec; ob += nthr * U) {
+        unsigned long long mine[U], old[U];
+        float y0[U];
+        uint32_t nn[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t o = ob + u * nthr;
+            nn[u] = 0xffffffffu;
+            if (o >= 32u * nvec) continue;
+            const uint32_t v = o >> 5, i = o & 31u;
+            float tot = 0.0f;
+            for (uint32_t rg = 0; rg < Ruse; ++rg) tot += cells[(size_t)i * stride + v + nvec * rg];
+            const uint32_t n = nbase + o;
+            nn[u] = n;
+            y0[u] = Tr<DT>::to_f(y[n]);
+            mine[u] = pack_partial(tot * Tr<DT>::to_f(sc[(size_t)(n & 7u) * wpr + (n >> 3)]));
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (nn[u] != 0xffffffffu) old[u] = atomicAdd(words + nn[u], mine[u]);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (nn[u] != 0xffffffffu) finish_packed<DT>(old[u], mine[u], arrivals, words + nn[u], y + nn[u], y0[u]);
+    }
+    DD_STAMP(cta, 3);
+}
+
 }  // namespace dd

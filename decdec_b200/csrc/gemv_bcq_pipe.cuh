@@ -54,7 +54,8 @@ struct PipeGeom {
     uint32_t a_bytes;        // alpha part of a stage
     uint32_t tile_stages;    // stages (128 outputs each) per output tile
     uint32_t smem_bytes;     // dynamic shared memory of the launch
-    uint32_t packed;         // 1: GEMV-only launch, sums and arrival counts travel in one 64-bit atomic per output
+    uint32_t packed;         // 1: sums and arrival counts travel in one 64-bit atomic per output (no tickets)
+    uint32_t arrivals;       // packed: arrivals that complete an output = 2 per K slice + 1 per compensation row part
     uint32_t wait_ns;        // limit of one bounded wait (DECDEC_PIPE_WAIT_NS)
     uint32_t test_skip_last; // test hook: the producer withholds its last stage, so that a wait runs out
 };
@@ -161,28 +162,6 @@ __device__ __forceinline__ void pipe_load_x8(const void* xbase, uint32_t k0, boo
 #pragma unroll
         for (int i = 0; i < 8; ++i) xv[i] = Tr<DT>::to_f(x[k0 + i]);
     }
-}
-
-// Packed accumulator word of a GEMV-only launch: bits 0..7 arrivals, 8..15 arrivals whose partial sum was not
-// finite, 16..63 the sum as signed fixed point with 20 fractional bits (finite partial sums are clamped to +-2^22).
-__device__ __forceinline__ unsigned long long pack_partial(float v) {
-    const bool finite = fabsf(v) <= 3.0e38f;      // false for inf and NaN
-    const float c = fminf(fmaxf(finite ? v : 0.0f, -4194304.0f), 4194304.0f);
-    const long long q = __float2ll_rn(c * 1048576.0f);
-    return ((unsigned long long)q << 16) + (finite ? 1ull : 0x101ull);
-}
-
-// The atomic of output n returned `old` when `mine` was added: if that was the last of `expected` arrivals, the
-// complete sum goes into y (y0 = the output's value read earlier) and the word is cleared for the next launch.
-template <int DT>
-__device__ __forceinline__ void finish_packed(unsigned long long old, unsigned long long mine, unsigned expected,
-                                              unsigned long long* word, typename Tr<DT>::T* yp, float y0) {
-    const unsigned long long now = old + mine;
-    if ((unsigned)(now & 0xffull) != expected) return;
-    const float sum = (float)((double)((long long)now >> 16) * (1.0 / 1048576.0));
-    const float out = ((now >> 8) & 0xffull) ? __int_as_float(0x7fc00000) : y0 + sum;
-    *yp = Tr<DT>::from_f(out);
-    __stcg(word, 0ull);
 }
 
 template <int DT, int BITS>
@@ -389,7 +368,7 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
                 atomicAdd(acc_lane + i * kPipeStageN, y1);
             } else {
                 // the previous stage's atomic has long returned: settle it, then send this stage's
-                if (pending) finish_packed<DT>(p_old, p_mine, 2u * p.n_kslices, p_word, p_y, p_y0);
+                if (pending) finish_packed<DT>(p_old, p_mine, geo.arrivals, p_word, p_y, p_y0);
                 const uint32_t n = (st0 + i) * kPipeStageN + n_out;
                 p_word = reinterpret_cast<unsigned long long*>(f.acc) + n;
                 p_y = reinterpret_cast<T*>(f.y) + n;
@@ -399,7 +378,7 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
                 pending = true;
             }
         }
-        if (pending) finish_packed<DT>(p_old, p_mine, 2u * p.n_kslices, p_word, p_y, p_y0);
+        if (pending) finish_packed<DT>(p_old, p_mine, geo.arrivals, p_word, p_y, p_y0);
     }
     DD_STAMP(cta + 256, 3);
     if (geo.packed) {

@@ -311,9 +311,24 @@ int run_bcq(Config* c, const void* x, void* y, const int32_t* qw, const void* al
         if (int r = fill_dec(c, x, true, f.n_tiles, &d)) return r;
         if (d.n_cta) { f.expected += d.n_rowparts; f.acc2 = ws.acc2; f.scales = d.scales; }
     }
-    // GEMV-only launches carry sums and arrival counts in one 64-bit atomic per output (the accumulator allocation
-    // holds kAccCap such words); DECDEC_BCQ_PACKED=0 keeps the ticket protocol
-    if (pipe) geo.packed = (d.n_cta == 0 && g.n_kslices <= 127u && env_u32("DECDEC_BCQ_PACKED", 1)) ? 1u : 0u;
+    // Launches of the pipelined kernel carry sums and arrival counts in one 64-bit atomic per output (the accumulator
+    // allocation holds kAccCap such words) instead of tickets; DECDEC_BCQ_PACKED=0 keeps the ticket protocol.  With a
+    // compensation role the CTA's private cells must fit in shared memory beside the selection state.
+    if (pipe && env_u32("DECDEC_BCQ_PACKED", 1)) {
+        const uint32_t arrivals = 2u * g.n_kslices + (d.n_cta ? d.n_rowparts : 0u);
+        bool ok = arrivals <= 255u;
+        if (ok && d.n_cta) {
+            const uint32_t tiles_max = cdiv(f.n_tiles, d.n_colparts);
+            const uint32_t nvec_max = cdiv(tiles_max * tile_units * 32u, 32u);
+            const uint32_t slots = nvec_max > (uint32_t)kPipeThreads ? nvec_max : (uint32_t)kPipeThreads;
+            const uint32_t need = (uint32_t)kDecPrivOff + (slots | 1u) * 128u;
+            // every output of a compensation CTA's column range costs it one atomic, and one SM issues about one per
+            // clock: beyond ~2048 outputs per CTA (few, wide compensation CTAs) the ticket protocol is faster
+            ok = (N % 32u) == 0u && need <= 227u * 1024u && nvec_max * 32u <= env_u32("DECDEC_PACKED_MAX_RANGE", 2048);
+            if (ok && geo.smem_bytes < need) geo.smem_bytes = need;
+        }
+        if (ok) { geo.packed = 1u; geo.arrivals = arrivals; }
+    }
     if (pipe) DD_CUDA(launch_bcq_pipe(dtype, g, d, f, geo, s));
     else DD_CUDA(launch_bcq(dtype, g, d, f, s));
     return 0;

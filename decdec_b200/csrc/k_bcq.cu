@@ -34,8 +34,12 @@ __global__ void __launch_bounds__(kPipeThreads, 1)
 k_bcq_pipe(const __grid_constant__ BcqParams g, const __grid_constant__ DecParams d, const __grid_constant__ FinParams f,
            const __grid_constant__ PipeGeom geo, const __grid_constant__ PipeMaps maps) {
     extern __shared__ __align__(128) unsigned char sm[];
-    if (blockIdx.x < d.n_cta) dec_role<DT>(d, f, blockIdx.x, sm);
-    else bcq_pipe_role<DT, BITS>(g, f, geo, maps, blockIdx.x - d.n_cta, sm);
+    if (blockIdx.x < d.n_cta) {
+        if (geo.packed) dec_role_packed<DT>(d, f, blockIdx.x, sm, geo.arrivals);
+        else dec_role<DT>(d, f, blockIdx.x, sm);
+    } else {
+        bcq_pipe_role<DT, BITS>(g, f, geo, maps, blockIdx.x - d.n_cta, sm);
+    }
 }
 
 // DECDEC_PDL: 0 = never, 1 = launches without a compensation role, 2 (default) = every launch
@@ -160,6 +164,7 @@ bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, in
     geo->smem_bytes = kPipeTblOffAssumed + kBcqTableBytes + after * geo->stage_bytes;
     if (geo->smem_bytes < (uint32_t)DecSmem::kBytes) geo->smem_bytes = DecSmem::kBytes;
     geo->packed = 0;                // set by the caller
+    geo->arrivals = 0;
     geo->wait_ns = env_u32_k("DECDEC_PIPE_WAIT_NS", 50u * 1000u * 1000u);
     geo->test_skip_last = env_u32_k("DECDEC_TEST_WITHHOLD_STAGE", 0) ? 1u : 0u;
     return true;

@@ -13,7 +13,10 @@ The JSON line reports tokens/s with compensation on (`value`), the same with com
 HBM roofline of the GEMV kernel, the host-link rate of the residual fetch, an end-to-end number with
 host buffers, and the reference's PyTorch CPU math timed on this box's cores.
 With --gpus N > 1 (launched by torchrun) the model is tensor-parallel: column-parallel wqkv/w1w3,
-row-parallel wo/w2 with an NCCL all-reduce; every rank fetches its own residual shard.
+row-parallel wo/w2 whose partial outputs are summed by one exchange per layer (a one-shot push kernel over
+NVLink peer memory by default, ncclAllReduce with --allreduce nccl); every rank fetches its own residual shard
+over its own host link.  The line also carries `config4`: the same measurement on Llama-3-70B shapes, the
+configuration that needs tensor parallelism.
 """
 from __future__ import annotations
 
@@ -37,33 +40,33 @@ MODELS = {
     "llama3-70b": (80, 8192, 64, 8, 128, 28672),
 }
 BITS, GROUP = 3, 128
-# (n_tb, k_chunk of wqkv, wo, w1w3, w2) chosen by `python -m decdec_b200.tuner` for a 5 % layer slowdown budget
-# on one B200 (profiles/tuner_llama3-8b.md); timed as an extra operating point beside k_chunk = 32
+# (n_tb, k_chunk of wqkv, wo, w1w3, w2): operating point chosen by `python -m decdec_b200.tuner` for a 5 % layer
+# slowdown budget on one B200; timed as an extra operating point beside k_chunk = 32
 TUNED_5PCT = {"llama3-8b": "16:0,0,5,3"}
-NCU_TRAFFIC_RATIO = 51.73 / 51.50   # measured DRAM bytes / algorithmic bytes of k_bcq_pipe, profiles/k_bcq_pipe_*.md
+# DRAM bytes read + written by one launch of the GEMV kernel on the 28672x4096 layer under ncu, divided by the
+# algorithmic bytes of that launch (51.73 MB / 51.50 MB): every weight byte is read once, so the traffic of other
+# launches is scaled from their algorithmic bytes with this ratio
+NCU_TRAFFIC_RATIO = 51.73 / 51.50
 
 
 def projections(model: str, tp: int = 1, rank: int = 0):
-    """[(name, N_local, K_local, parallel)] of one layer; fused wqkv / w1w3 as in the reference model
-    (end-to-end/model.py:266,331)."""
+    """One layer's projections as dicts {name, n, k, par, n_full, n0}: n x k is this rank's GEMV, n_full the width
+    of the layer's output vector and n0 where this rank's outputs start in it.  Fused wqkv / w1w3 as in the
+    reference model (end-to-end/model.py:266,331); column-parallel wqkv / w1w3, row-parallel wo / w2 cut at
+    selection-chunk boundaries (decdec_b200.tp.row_plan)."""
     from decdec_b200 import tp as tpl
     _, d, hq, hkv, hd, ffn = MODELS[model]
     qkv = (hq + 2 * hkv) * hd
 
-    def col(n):
+    def col(name, n, k):
         a, b = tpl.split_even(n, tp, 128 if n % (128 * tp) == 0 else 32)[rank]
-        return b - a
+        return dict(name=name, n=b - a, k=k, par="col", n_full=b - a, n0=0)
 
-    def row(k):
-        a, b = tpl.k_ranges(k, tp, GROUP)[rank]
-        return b - a
+    def row(name, n, k):
+        k0, k1, n0, n1 = tpl.row_plan(k, n, tp)[rank]
+        return dict(name=name, n=n1 - n0, k=k1 - k0, par="row", n_full=n, n0=n0)
 
-    return [
-        ("wqkv", col(qkv), d, "col"),
-        ("wo", d, row(d), "row"),
-        ("w1w3", col(2 * ffn), d, "col"),
-        ("w2", d, row(ffn), "row"),
-    ]
+    return [col("wqkv", qkv, d), row("wo", d, d), col("w1w3", 2 * ffn, d), row("w2", d, ffn)]
 
 
 def gemv_bytes(n, k):
@@ -126,65 +129,100 @@ class ClockSampler:
 # reference arm / CPU baseline: the reference's PyTorch math on host cores
 # --------------------------------------------------------------------------------------------------
 
-def cpu_sample(model: str, k_chunk: int, reps: int, warm: int):
-    """Times the reference's CPU path (dequantise every call, exact per-chunk top-k, two mat-vecs;
-    oracle/forward.py) on a bounded sample: the `wo` projection (hidden x hidden) of one layer.
-    Returns (seconds per sample, sample description, scale = weights per token / weights in sample)."""
+CPU_ROWS = 2048      # outputs per projection in the timed CPU sample (cost is linear in the outputs)
+
+
+def cpu_layer_sample(model: str, k_chunk: int):
+    """Tensors of ONE layer for the CPU path: the four projection shapes with at most CPU_ROWS outputs each.
+    Returns [(name, n_full, n_sample, k, tensors)]."""
+    import torch
+    out = []
+    g = torch.Generator().manual_seed(0)
+    for p in projections(model):
+        n, k = p["n"], p["k"]
+        ns = min(n, CPU_ROWS)
+        qw = torch.randint(-2**31, 2**31 - 1, (k // 32, BITS, ns), dtype=torch.int32, generator=g)
+        alpha = (torch.rand(k // GROUP, BITS, ns, generator=g) * 0.01).half()
+        qb = ((torch.rand(k // GROUP, ns, generator=g) - 0.5) * 0.01).half()
+        cs = torch.randint(-2**31, 2**31 - 1, (k, ns // 8), dtype=torch.int32, generator=g)
+        sc = (torch.rand(ns, generator=g) * 1e-3).half()
+        x = torch.randn(k, generator=g)
+        out.append((p["name"], n, ns, k, (qw, alpha, qb, cs, sc, x)))
+    return out
+
+
+def cpu_time_layer(sample, k_chunk: int, predequant):
+    """Seconds for one decode step of one layer on the CPU, every projection scaled from its sampled outputs to its
+    full width.  predequant = list of (W^T, R^T) prepared beforehand, or None for the reference modules' behaviour
+    (dequantise at every call, end-to-end/LUTGEMMLinear.py:41-82)."""
+    from oracle import forward as ofw
+    total, raw = 0.0, 0.0
+    for i, (_, n, ns, k, (qw, alpha, qb, cs, sc, x)) in enumerate(sample):
+        t0 = time.perf_counter()
+        if predequant is None:
+            wt = ofw.torch_bcq_dequant(qw, alpha, qb, GROUP)
+            rt = ofw.torch_unpack_residual(cs, sc) if k_chunk else None
+        else:
+            wt, rt = predequant[i]
+        ofw.cpu_reference_linear(x, wt, rt, k_chunk)
+        dt = time.perf_counter() - t0
+        raw += dt
+        total += dt * (n / ns)
+    return total, raw
+
+
+def cpu_baseline(model: str, k_chunk: int, reps: int, warm: int):
+    """Median per-token time of the reference's CPU math: BCQ dequant + residual unpack + exact per-chunk top-k +
+    two mat-vecs (oracle/forward.py), both dequantising at every call and with the dense matrices prepared once."""
     import torch
     from oracle import forward as ofw
-    layers, d, *_ = MODELS[model]
-    n = k = d
-    g = torch.Generator().manual_seed(0)
-    qw = torch.randint(-2**31, 2**31 - 1, (k // 32, BITS, n), dtype=torch.int32, generator=g)
-    alpha = (torch.rand(k // GROUP, BITS, n, generator=g) * 0.01).half()
-    qb = ((torch.rand(k // GROUP, n, generator=g) - 0.5) * 0.01).half()
-    cs = torch.randint(-2**31, 2**31 - 1, (k, n // 8), dtype=torch.int32, generator=g)
-    sc = (torch.rand(n, generator=g) * 1e-3).half()
-    x = torch.randn(k, generator=g)
-
-    def once():
-        wt = ofw.torch_bcq_dequant(qw, alpha, qb, GROUP)
-        rt = ofw.torch_unpack_residual(cs, sc) if k_chunk else None
-        return ofw.cpu_reference_linear(x, wt, rt, k_chunk)
-
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))      # torchrun pins its ranks to one OpenMP thread
+    except (AttributeError, RuntimeError):
+        pass
+    layers = MODELS[model][0]
+    sample = cpu_layer_sample(model, k_chunk)
+    pre = [(ofw.torch_bcq_dequant(t[0], t[1], t[2], GROUP), ofw.torch_unpack_residual(t[3], t[4]) if k_chunk else None)
+           for *_, t in sample]
     for _ in range(warm):
-        once()
-    ts = []
-    for _ in range(reps):
-        t0 = time.perf_counter(); once(); ts.append(time.perf_counter() - t0)
-    per_token = layers * sum(nn * kk for _, nn, kk, _ in projections(model))
-    return ts, f"wo projection {n}x{k} of one layer: BCQ dequant + residual unpack + per-chunk top-k + 2 matvec, fp32", per_token / (n * k)
+        cpu_time_layer(sample, k_chunk, None)
+        cpu_time_layer(sample, k_chunk, pre)
+    every_raw = [cpu_time_layer(sample, k_chunk, None) for _ in range(reps)]
+    once_raw = [cpu_time_layer(sample, k_chunk, pre) for _ in range(reps)]
+    every, once = [t for t, _ in every_raw], [t for t, _ in once_raw]
+    desc = (f"one layer of {model} (wqkv, wo, w1w3, w2), {CPU_ROWS} of each projection's outputs timed and scaled to its width, "
+            f"then x{layers} layers: BCQ dequant + residual unpack + per-chunk top-k + 2 matvec in fp32; median of {reps} repetitions; "
+            "the token time is extrapolated from this sample, not run in full")
+    return {"s_per_token_dequant_every_call": statistics.median(every) * layers,
+            "s_per_token_predequantised": statistics.median(once) * layers,
+            "measured_wall_s": sum(r for _, r in every_raw), "cores": torch.get_num_threads(), "sample": desc}
 
 
 def run_reference(args):
-    import torch
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    # torchrun sets OMP_NUM_THREADS=1 for its ranks; the CPU arm uses every core this process may run on
-    try:
-        torch.set_num_threads(len(os.sched_getaffinity(0)))
-    except (AttributeError, RuntimeError):
-        pass
-    cores = torch.get_num_threads()
-    ts, desc, scale = cpu_sample(args.model, args.k_chunk, args.steps, max(1, args.warmup))
-    total = sum(ts)
-    tok_s = len(ts) / (total * scale)
+    r = cpu_baseline(args.model, args.k_chunk, max(args.steps, 10), max(1, args.warmup))
+    tok_s = 1.0 / r["s_per_token_dequant_every_call"]
     line = {
         "impl": "reference", "metric": "batch-1 decode tok/s (DecDEC on)", "value": tok_s, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(ts) * scale,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * r["s_per_token_dequant_every_call"],
+        "measured_wall_s": r["measured_wall_s"],
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args),
-        "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc + f"; scaled x{scale:.0f} to a token"},
+        "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"],
+                         "predequantised_tokens_per_s": 1.0 / r["s_per_token_predequantised"]},
         "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
 
 
-def workload_config(args):
-    layers, d, hq, hkv, hd, ffn = MODELS[args.model]
-    return {"workload": f"{args.model} decode hot path: {layers} layers x (wqkv, wo, w1w3, w2) fused GEMV+DEC, "
-                        f"{BITS}-bit binary-coded group-{GROUP} weights, 4-bit residual rows in pinned host memory",
+def workload_config(args, model=None):
+    model = model or args.model
+    layers, d, hq, hkv, hd, ffn = MODELS[model]
+    return {"workload": f"{model} decode hot path: {layers} layers x (wqkv, wo, w1w3, w2) fused GEMV+DEC, "
+                        f"{BITS}-bit binary-coded group-{GROUP} weights, 4-bit residual rows in pinned host memory; "
+                        "linears only (attention, norms and lm_head are not part of the measured path)",
             "k_chunk": args.k_chunk, "n_tb": args.n_tb, "batch": 1,
             "parallelism": (f"tp{args.gpus}, row-parallel outputs summed by " + ("a one-shot push kernel over NVLink peer memory"
                             if args.allreduce == "push" else "ncclAllReduce")) if args.gpus > 1 else "single",
@@ -195,61 +233,236 @@ def workload_config(args):
 # our arm
 # --------------------------------------------------------------------------------------------------
 
-def build_model(args, torch, ext, dev, rank, tp):
-    """Random packed tensors of the model's shapes; one storage per layer and projection."""
-    layers = MODELS[args.model][0]
-    if args.layers:
-        layers = args.layers
-    g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    gc = torch.Generator().manual_seed(99 + rank)
-    rows = torch.zeros(32 * 1024, dtype=torch.int32, device=dev)
-    acts = torch.zeros(32 * 1024, dtype=torch.float16, device=dev)
-    ctx = ext.create_dec_context(args.n_tb, rows, acts)
-    proj = projections(args.model, tp, rank)
-    # one random residual per projection shape on the host; every config pins its own copy
-    host_res = {}
-    for name, n, k, _ in proj:
-        host_res[name] = (torch.randint(-2**31, 2**31 - 1, (k, n // 8), dtype=torch.int32, generator=gc),
-                          (torch.rand(n, generator=gc) * 1e-3 + 1e-4).half(),
-                          torch.sort(torch.randn(k, generator=gc).abs() * 3, descending=True).values.half())
-    model = []
-    for _ in range(layers):
-        layer = []
-        for name, n, k, par in proj:
-            qw = torch.randint(-2**31, 2**31 - 1, (k // 32, BITS, n), dtype=torch.int32, device=dev, generator=g)
-            alpha = (torch.rand(k // GROUP, BITS, n, device=dev, generator=g) * 0.01).half()
-            qb = ((torch.rand(k // GROUP, n, device=dev, generator=g) - 0.5) * 0.01).half()
-            q, sc, thr = host_res[name]
-            cfg_on = ext.create_dec_config(ctx, args.k_chunk, q, sc, thr)
-            layer.append(dict(name=name, n=n, k=k, par=par, qw=qw, alpha=alpha, qb=qb, cfg=cfg_on, thr=thr))
-        model.append(layer)
-    # all layer outputs live in one buffer that is cleared once per token (the entry points accumulate
-    # into their output; the reference's modules clear each output with its own kernel before every call)
-    total = sum(p["n"] for layer in model for p in layer)
-    ybuf = torch.zeros(total, dtype=torch.float16, device=dev)
-    off = 0
-    for layer in model:
-        for p in layer:
-            p["y"] = ybuf[off:off + p["n"]].view(1, 1, p["n"])
-            off += p["n"]
-    return model, ctx, (rows, acts, ybuf, host_res)
+class Workload:
+    """The quantized linears of one model on this rank: random packed tensors of the model's shapes (one storage per
+    layer and projection), their compensation configs, CUDA graphs of one token per mode, and event timing."""
+
+    def __init__(self, env, model_name, k_chunk, n_tb, layers=0, resident=False):
+        torch, ext = env["torch"], env["ext"]
+        self.env, self.name, self.k_chunk = env, model_name, k_chunk
+        dev, rank, tp = env["dev"], env["rank"], env["world"]
+        n_layers = layers or MODELS[model_name][0]
+        g = torch.Generator(device=dev).manual_seed(1234 + rank)
+        gc = torch.Generator().manual_seed(99 + rank)
+        self.rows = torch.zeros(32 * 1024, dtype=torch.int32, device=dev)
+        self.acts = torch.zeros(32 * 1024, dtype=torch.float16, device=dev)
+        self.ctx = ext.create_dec_context(n_tb, self.rows, self.acts)
+        proj = projections(model_name, tp, rank)
+        # one random residual per projection shape on the host; every config pins its own copy
+        self.host_res = {}
+        for p in proj:
+            n, k = p["n"], p["k"]
+            self.host_res[p["name"]] = (torch.randint(-2**31, 2**31 - 1, (k, n // 8), dtype=torch.int32, generator=gc),
+                                        (torch.rand(n, generator=gc) * 1e-3 + 1e-4).half(),
+                                        torch.sort(torch.randn(k, generator=gc).abs() * 3, descending=True).values.half())
+        self.model = []
+        for _ in range(n_layers):
+            layer = []
+            for p in proj:
+                n, k = p["n"], p["k"]
+                q, sc, thr = self.host_res[p["name"]]
+                e = dict(p)
+                e["qw"] = torch.randint(-2**31, 2**31 - 1, (k // 32, BITS, n), dtype=torch.int32, device=dev, generator=g)
+                e["alpha"] = (torch.rand(k // GROUP, BITS, n, device=dev, generator=g) * 0.01).half()
+                e["qb"] = ((torch.rand(k // GROUP, n, device=dev, generator=g) - 0.5) * 0.01).half()
+                e["cfg"] = ext.create_dec_config(self.ctx, k_chunk, q.to(dev) if resident else q, sc, thr)
+                e["thr"] = thr
+                layer.append(e)
+            self.model.append(layer)
+        # all layer outputs live in one buffer that is cleared once per token (the entry points accumulate into their
+        # output; the reference's modules clear each output with its own kernel before every call).  A row-parallel
+        # rank writes its partial sums into its range of the layer's full-width vector, which is then summed over ranks.
+        total = sum(p["n_full"] for layer in self.model for p in layer)
+        self.ybuf = torch.zeros(total, dtype=torch.float16, device=dev)
+        off = 0
+        for layer in self.model:
+            for p in layer:
+                p["y_full"] = self.ybuf[off:off + p["n_full"]]
+                p["y"] = p["y_full"][p["n0"]:p["n0"] + p["n"]].view(1, 1, p["n"])
+                off += p["n_full"]
+        # activation sets (N(0,1) with 1% x20 outliers) per input width, rotated between steps so that the selected
+        # rows change from token to token
+        gi = torch.Generator().manual_seed(7)
+        self.widths = sorted({p["k"] for p in self.model[0]})
+        self.in_sets = []
+        for _ in range(4):
+            st = {}
+            for k in self.widths:
+                x = torch.randn(k, generator=gi)
+                idx = torch.randperm(k, generator=gi)[: max(1, k // 100)]
+                x[idx] *= 20
+                st[k] = x.half().reshape(1, 1, k)
+            self.in_sets.append(st)
+        self.xbuf = {k: torch.zeros(1, 1, k, dtype=torch.float16, device=dev) for k in self.widths}
+        self.pinned_in = [{k: v.pin_memory() for k, v in st.items()} for st in self.in_sets]
+        self.dev_sets = [{k: v.to(dev) for k, v in st.items()} for st in self.in_sets]
+        self.out_host = torch.zeros(1, 1, self.model[-1][-1]["n"], dtype=torch.float16).pin_memory()
+        self.stream = torch.cuda.Stream()
+        self.graphs = {}
+
+    # ---- one token ------------------------------------------------------------------------------------------
+    def token(self, mode):
+        """All quantized linears of one token.  mode: "on" (fused GEMV + compensation), "off" (GEMV only),
+        "gemv" (GEMV only and no exchange between ranks), "xchg" (the exchanges alone).  Inputs come from fixed
+        activation buffers (the glue between the linears is not part of the measured path)."""
+        ext, allreduce = self.env["ext"], self.env["allreduce"]
+        self.ybuf.zero_()
+        for layer in self.model:
+            for p in layer:
+                if mode == "on":
+                    ext.dec_lutgemm(p["cfg"], self.xbuf[p["k"]], p["y"], p["qw"], p["alpha"], p["qb"], BITS, GROUP)
+                elif mode in ("off", "gemv"):
+                    ext.lutgemm_gemv(self.xbuf[p["k"]], p["y"], p["qw"], p["alpha"], p["qb"], BITS, GROUP)
+                if p["par"] == "row" and allreduce is not None and mode != "gemv":
+                    allreduce(p["y_full"])
+
+    def load_inputs(self, i):
+        for k in self.widths:
+            self.xbuf[k].copy_(self.pinned_in[i % len(self.pinned_in)][k], non_blocking=True)
+
+    def capture(self, key, mode):
+        torch = self.env["torch"]
+        with torch.cuda.stream(self.stream):
+            self.load_inputs(0)
+            self.token(mode)                 # outside capture: allocates the library workspace of this stream
+            self.stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self.stream):
+                self.token(mode)
+            self.graphs[key] = g
+        torch.cuda.synchronize()
+
+    def retune(self, n_tb, k_chunks):
+        """Re-point every config at a context with another thread-block budget and per-projection k_chunk (launch
+        arguments are baked into graphs already captured, so this only affects later captures)."""
+        ext = self.env["ext"]
+        ctx = ext.create_dec_context(n_tb, self.rows, self.acts)
+        for layer in self.model:
+            for p, kc in zip(layer, k_chunks):
+                ext.update_dec_config(p["cfg"], ctx, kc)
+        return ctx
+
+    def timed(self, key, steps, warm, e2e=False):
+        """`steps` graph replays timed with CUDA events on the launching stream; max over ranks."""
+        torch, dist, dev = self.env["torch"], self.env["dist"], self.env["dev"]
+        g = self.graphs[key]
+
+        def barrier():
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        with torch.cuda.stream(self.stream):
+            for i in range(warm):
+                self.load_inputs(i)
+                g.replay()
+            self.stream.synchronize()
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if not e2e:
+                # inputs already resident: rotate device-side activation sets without host traffic
+                a.record(self.stream)
+                for i in range(steps):
+                    for k in self.widths:
+                        self.xbuf[k].copy_(self.dev_sets[i % len(self.dev_sets)][k], non_blocking=True)
+                    g.replay()
+                b.record(self.stream)
+            else:
+                a.record(self.stream)
+                for i in range(steps):
+                    self.load_inputs(i)                                          # H2D from pinned host memory
+                    g.replay()
+                    self.out_host.copy_(self.model[-1][-1]["y"], non_blocking=True)   # D2H of the step's result
+                    self.stream.synchronize()
+                b.record(self.stream)
+            self.stream.synchronize()
+        barrier()
+        ms = a.elapsed_time(b)
+        if dist is not None:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    # ---- bytes ----------------------------------------------------------------------------------------------
+    def hbm_bytes(self):
+        return len(self.model) * sum(gemv_bytes(p["n"], p["k"]) for p in self.model[0])
+
+    def link_bytes(self, k_chunks=None):
+        ks = k_chunks or [self.k_chunk] * len(self.model[0])
+        return len(self.model) * sum(fetch_bytes(p["n"], p["k"], kc) for p, kc in zip(self.model[0], ks))
+
+    def calls(self):
+        return len(self.model) * len(self.model[0])
+
+    def exchanges(self):
+        return len(self.model) * sum(1 for p in self.model[0] if p["par"] == "row")
+
+    def close(self):
+        ext = self.env["ext"]
+        self.graphs.clear()
+        self.env["torch"].cuda.synchronize()
+        for layer in self.model:
+            for p in layer:
+                ext.destroy_dec_config(p["cfg"])
+        self.model = []
 
 
-def make_inputs(torch, model, dev, n_sets=4):
-    """Activation sets (N(0,1) with 1% x20 outliers) per input width, rotated between steps so that
-    the selected rows change from token to token."""
-    g = torch.Generator().manual_seed(7)
-    widths = sorted({p["k"] for p in model[0]})
-    sets = []
-    for _ in range(n_sets):
-        s = {}
-        for k in widths:
-            x = torch.randn(k, generator=g)
-            idx = torch.randperm(k, generator=g)[: max(1, k // 100)]
-            x[idx] *= 20
-            s[k] = x.half().reshape(1, 1, k)
-        sets.append(s)
-    return widths, sets
+def all_ranks_sum(env, v):
+    if env["dist"] is None:
+        return v
+    t = env["torch"].tensor([float(v)], device=env["dev"], dtype=env["torch"].float64)
+    env["dist"].all_reduce(t)
+    return float(t.item())
+
+
+def measure(env, args, model_name, layers, steps, warm, extras):
+    """on / off / GEMV-only / exchange timings of one model; `extras` adds e2e, the tuned and the resident operating points."""
+    world = env["world"]
+    n_tb = args.n_tb if world == 1 else max(16, args.n_tb // world)     # the compensation budget shrinks with the shard
+    w = Workload(env, model_name, args.k_chunk, n_tb, layers)
+    out = {"n_tb": n_tb, "layers": len(w.model)}
+    w.capture("on", "on")
+    w.capture("off", "off")
+    out["ms_on"] = w.timed("on", steps, warm)
+    out["ms_off"] = w.timed("off", steps, warm)
+    if world > 1:
+        w.capture("gemv", "gemv")
+        w.capture("xchg", "xchg")
+        out["ms_gemv"] = w.timed("gemv", steps, warm)
+        out["ms_xchg"] = w.timed("xchg", steps, warm)
+    else:
+        out["ms_gemv"] = out["ms_off"]
+    if extras:
+        out["ms_e2e"] = w.timed("on", steps, warm, e2e=True)
+        out["h2d"] = sum(2 * k for k in w.widths)
+        out["d2h"] = w.out_host.numel() * 2
+    out["hbm_bytes"] = all_ranks_sum(env, w.hbm_bytes())                  # all ranks' GEMV bytes of a step
+    out["link_bytes"] = all_ranks_sum(env, w.link_bytes())
+    out["link_bytes_rank"] = w.link_bytes()
+    out["calls"] = w.calls()
+    out["exchanges"] = w.exchanges() if world > 1 else 0
+    tuned = args.tuned if args.tuned is not None else (TUNED_5PCT.get(model_name, "") if world == 1 else "")
+    if extras and tuned:
+        n_tb_t, ks = tuned.split(":")
+        ks = [int(v) for v in ks.split(",")]
+        w.retune(int(n_tb_t), ks)
+        w.capture("tuned", "on")
+        out["tuned"] = {"ms": w.timed("tuned", steps, warm), "n_tb": int(n_tb_t),
+                        "k_chunk": dict(zip([p["name"] for p in w.model[0]], ks)), "bytes": w.link_bytes(ks)}
+    w.close()
+    del w
+    env["torch"].cuda.empty_cache()
+    if extras and world == 1 and not args.no_resident:
+        # the same compensation with the residual resident in HBM (3.5 GB for Llama-3-8B, which a 180 GB part can
+        # afford): what is left of the cost once the host link is out of the picture
+        wr = Workload(env, model_name, args.k_chunk, args.resident_n_tb, layers, resident=True)
+        wr.capture("on", "on")
+        out["resident"] = {"ms": wr.timed("on", steps, warm), "n_tb": args.resident_n_tb}
+        wr.close()
+        del wr
+        env["torch"].cuda.empty_cache()
+    return out
 
 
 def run_micro(args):
@@ -348,8 +561,10 @@ def main():
     ap.add_argument("--resident-n-tb", type=int, default=32, help="thread-block budget of the residual-in-HBM operating point")
     ap.add_argument("--no-resident", action="store_true",
                     help="skip the extra operating point with the residual held in HBM instead of pinned host memory")
-    ap.add_argument("--allreduce", default="nccl", choices=["push", "nccl"],
+    ap.add_argument("--allreduce", default="push", choices=["push", "nccl"],
                     help="multi-GPU: exchange of the row-parallel outputs (push = one-shot kernel over NVLink peer memory)")
+    ap.add_argument("--no-config4", action="store_true", help="skip the Llama-3-70B-shaped measurement")
+    ap.add_argument("--config4-layers", type=int, default=0, help="layers of the Llama-3-70B-shaped model (0 = all 80)")
     ap.add_argument("--micro", default="", help="single entry point: lutgemm | dec_lutgemm | anyprec | dec_anyprec | sqllm | dec")
     ap.add_argument("--n", type=int, default=28672)
     ap.add_argument("--k", type=int, default=4096)
@@ -376,152 +591,29 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    tp = world
     allreduce = None
     if dist is not None:
         if args.allreduce == "push":
             from decdec_b200.tp import PushAllReduce
-            allreduce = PushAllReduce(max(MODELS[args.model][1], 1024))
+            allreduce = PushAllReduce(max(max(m[1] for m in MODELS.values()), 1024))
         else:
             allreduce = dist.all_reduce
-
-    model, ctx, _keep = build_model(args, torch, ext, dev, rank, tp)
-    widths, in_sets = make_inputs(torch, model, dev)
+    env = dict(torch=torch, ext=ext, dev=dev, rank=rank, world=world, dist=dist, allreduce=allreduce)
     if dist is not None:
         # ranks finish their set-up seconds apart; the push exchange waits for a peer for about a second only
         dist.barrier()
         torch.cuda.synchronize()
-    xbuf = {k: torch.zeros(1, 1, k, dtype=torch.float16, device=dev) for k in widths}
-    pinned_in = [{k: v.pin_memory() for k, v in s.items()} for s in in_sets]
-    out_host = torch.zeros(1, 1, model[0][-1]["n"], dtype=torch.float16).pin_memory()
-
-    def token(on: bool):
-        """All quantized linears of one token.  Inputs come from fixed activation buffers (attention,
-        norms and the element-wise glue between the linears are not part of the measured path)."""
-        _keep[2].zero_()
-        for layer in model:
-            for p in layer:
-                if on:
-                    ext.dec_lutgemm(p["cfg"], xbuf[p["k"]], p["y"], p["qw"], p["alpha"], p["qb"], BITS, GROUP)
-                else:
-                    ext.lutgemm_gemv(xbuf[p["k"]], p["y"], p["qw"], p["alpha"], p["qb"], BITS, GROUP)
-                if p["par"] == "row" and allreduce is not None:
-                    allreduce(p["y"])
-
-    def load_inputs(i):
-        for k in widths:
-            xbuf[k].copy_(pinned_in[i % len(pinned_in)][k], non_blocking=True)
-
-    # warm-up outside capture (allocates the library workspace), then capture one token per mode
-    stream = torch.cuda.Stream()
-    graphs = {}
-    with torch.cuda.stream(stream):
-        load_inputs(0)
-        for on in (True, False):
-            token(on)
-        stream.synchronize()
-        for on in (True, False):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                token(on)
-            graphs[on] = g
-        # extra operating point: per-projection k_chunk and a smaller thread-block budget.  The configs are
-        # re-pointed in place (launch arguments are baked into the graphs captured above).
-        tuned = args.tuned if args.tuned is not None else (TUNED_5PCT.get(args.model, "") if world == 1 else "")
-        tuned_cfg = None
-        if tuned:
-            n_tb_t, ks = tuned.split(":")
-            ks = [int(v) for v in ks.split(",")]
-            tuned_cfg = {"n_tb": int(n_tb_t), "k_chunk": dict(zip([p["name"] for p in model[0]], ks))}
-            ctx_t = ext.create_dec_context(int(n_tb_t), _keep[0], _keep[1])
-            for layer in model:
-                for p, kc in zip(layer, ks):
-                    ext.update_dec_config(p["cfg"], ctx_t, kc)
-            token(True)
-            stream.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                token(True)
-            graphs["tuned"] = g
-        # extra operating point: the same compensation with the residual resident in HBM (3.5 GB for this model, which a
-        # 180 GB part can afford) - what is left of the cost once the host link is out of the picture
-        if world == 1 and not args.no_resident:
-            dev_cfgs = []
-            ctx_r = ext.create_dec_context(args.resident_n_tb, _keep[0], _keep[1])
-            for layer in model:
-                for p in layer:
-                    q, sc, thr = _keep[3][p["name"]]
-                    dev_cfgs.append(ext.create_dec_config(ctx_r, args.k_chunk, q.to(dev), sc, thr))
-
-            def token_resident():
-                _keep[2].zero_()
-                i = 0
-                for layer in model:
-                    for p in layer:
-                        ext.dec_lutgemm(dev_cfgs[i], xbuf[p["k"]], p["y"], p["qw"], p["alpha"], p["qb"], BITS, GROUP)
-                        i += 1
-
-            token_resident()
-            stream.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                token_resident()
-            graphs["resident"] = g
-    torch.cuda.synchronize()
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(on: bool, steps: int, warm: int, e2e: bool):
-        """K graph replays timed with CUDA events on the launching stream; max over ranks."""
-        with torch.cuda.stream(stream):
-            for i in range(warm):
-                load_inputs(i)
-                graphs[on].replay()
-            stream.synchronize()
-            barrier()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            if not e2e:
-                # inputs already resident: rotate device-side activation sets without host traffic
-                dev_sets = [{k: v.to(dev) for k, v in s.items()} for s in in_sets]
-                stream.synchronize()
-                a.record(stream)
-                for i in range(steps):
-                    for k in widths:
-                        xbuf[k].copy_(dev_sets[i % len(dev_sets)][k], non_blocking=True)
-                    graphs[on].replay()
-                b.record(stream)
-            else:
-                a.record(stream)
-                for i in range(steps):
-                    load_inputs(i)                                     # H2D from pinned host memory
-                    graphs[on].replay()
-                    out_host.copy_(model[-1][-1]["y"], non_blocking=True)   # D2H of the step's result
-                    stream.synchronize()
-                b.record(stream)
-            stream.synchronize()
-        barrier()
-        ms = a.elapsed_time(b)
-        if dist is not None:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms / steps
 
     sampler = ClockSampler(local) if rank == 0 else None
-    ms_on = timed(True, args.steps, args.warmup, e2e=False)
-    ms_off = timed(False, args.steps, args.warmup, e2e=False)
-    ms_e2e = timed(True, args.steps, args.warmup, e2e=True)
-    ms_tuned = timed("tuned", args.steps, args.warmup, e2e=False) if "tuned" in graphs else None
-    ms_res = timed("resident", args.steps, args.warmup, e2e=False) if "resident" in graphs else None
+    r = measure(env, args, args.model, args.layers, args.steps, args.warmup, extras=True)
+    c4 = None
+    if not args.no_config4 and args.model != "llama3-70b":
+        try:
+            c4 = measure(env, args, "llama3-70b", args.config4_layers, max(3, args.steps // 2), 3, extras=False)
+        except RuntimeError as e:      # e.g. the pinned host memory for 80 layers of residuals could not be had
+            c4 = {"unavailable": str(e).splitlines()[0][:200]}
     clocks = sampler.stop() if sampler else {}      # sampled across all timed regions of the run
 
-    n_layers = len(model)
-    calls = n_layers * len(model[0])
-    hbm_bytes = n_layers * sum(gemv_bytes(p["n"], p["k"]) for p in model[0])
-    link_bytes = n_layers * sum(fetch_bytes(p["n"], p["k"], args.k_chunk) for p in model[0])
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -529,60 +621,74 @@ def main():
         pass
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
     peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s"
-    gemv_gbs = hbm_bytes / (ms_off * 1e-3) / 1e9
-    link_gbs = link_bytes / (ms_on * 1e-3) / 1e9
-    h2d = sum(2 * k for k in widths)
-    d2h = out_host.numel() * 2
+
+    def roofline(m):
+        gbs = m["hbm_bytes"] / (m["ms_gemv"] * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": gbs, "peak": hbm_peak * world, "unit": "GB/s", "frac": gbs / (hbm_peak * world),
+                "traffic": NCU_TRAFFIC_RATIO * m["hbm_bytes"] / (m["calls"] * world),
+                "traffic_note": "scaled from the algorithmic bytes with the DRAM/algorithmic ratio of one profiled launch (28672x4096), not measured in this run",
+                "kernel": "k_bcq_pipe<fp16,3> (GEMV role, compensation off, no exchange between ranks)",
+                "launches_per_step": m["calls"], "algorithmic_bytes_per_step": m["hbm_bytes"], "peak_source": peak_src + (f" x {world} GPUs" if world > 1 else ""),
+                "frac_of_spec_8000": gbs / (8000.0 * world),
+                "note": "bytes of all GEMV launches of a step (all ranks) / event-timed duration of the GEMV-only step"}
+
+    def summary(m):
+        d = {"on": {"value": 1e3 / m["ms_on"], "unit": "tokens/s", "ms_per_step": m["ms_on"]},
+             "off": {"value": 1e3 / m["ms_off"], "unit": "tokens/s", "ms_per_step": m["ms_off"]},
+             "slowdown_on_vs_off": m["ms_on"] / m["ms_off"], "layers": m["layers"], "n_tb": m["n_tb"],
+             "roofline": roofline(m),
+             "host_link": {"achieved_all_ranks": m["link_bytes"] / (m["ms_on"] * 1e-3) / 1e9,
+                           "achieved_per_rank": m["link_bytes_rank"] / (m["ms_on"] * 1e-3) / 1e9, "unit": "GB/s", "peak_spec_per_rank": 64.0,
+                           "fetched_bytes_per_step": m["link_bytes"]}}
+        if world > 1:
+            d["exchange"] = {"kind": args.allreduce, "calls_per_step": m["exchanges"], "us_per_call": 1e3 * m["ms_xchg"] / max(1, m["exchanges"]),
+                             "ms_per_step_alone": m["ms_xchg"], "gemv_only_ms_per_step": m["ms_gemv"]}
+        return d
 
     if rank == 0:
-        cpu = None
-        if not args.no_cpu_baseline:
-            try:
-                torch.set_num_threads(len(os.sched_getaffinity(0)))      # torchrun pins ranks to one OpenMP thread
-            except (AttributeError, RuntimeError):
-                pass
-            ts, desc, scale = cpu_sample(args.model, args.k_chunk, 5, 1)
-            cpu = {"value": len(ts) / (sum(ts) * scale), "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-                   "sample": desc + f"; 5 repetitions, scaled x{scale:.0f} to a token"}
+        ms_on, ms_off = r["ms_on"], r["ms_off"]
+        link_gbs = r["link_bytes"] / (ms_on * 1e-3) / 1e9
         line = {
             "metric": "batch-1 decode tok/s (DecDEC on)", "value": 1e3 / ms_on, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_on, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16 in/out, f32 accumulate", "data": "synthetic",
             "config": workload_config(args),
-            "decdec_off": {"value": 1e3 / ms_off, "unit": "tokens/s", "ms_per_step": ms_off,
-                           "slowdown_on_vs_off": ms_on / ms_off},
-            "roofline": {"bound": "hbm", "achieved": gemv_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gemv_gbs / hbm_peak,
-                         # ncu capture of the w1w3 launch (profiles/): dram read+write 51.73 MB for 51.50 MB algorithmic
-                         "traffic": NCU_TRAFFIC_RATIO * hbm_bytes / calls, "kernel": "k_bcq_pipe<fp16,3> (GEMV role, compensation off)", "launches_per_step": calls,
-                         "algorithmic_bytes_per_step": hbm_bytes, "peak_source": peak_src, "frac_of_spec_8000": gemv_gbs / 8000.0,
-                         "note": "bytes of all GEMV launches of a step / event-timed duration of the step with compensation off"},
-            "host_link": {"achieved": link_gbs, "unit": "GB/s", "peak_spec": 64.0, "frac_of_spec": link_gbs / 64.0,
-                          "measured_h2d_memcpy_peak": 55.4, "fetched_bytes_per_step": link_bytes,
-                          "note": "residual bytes of a step / event-timed duration of the step with compensation on (lower bound of the link rate)"},
-            "e2e": {"value": 1e3 / ms_e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": ms_e2e},
-            "gpu_launches": calls * args.steps,
+            "decdec_off": {"value": 1e3 / ms_off, "unit": "tokens/s", "ms_per_step": ms_off, "slowdown_on_vs_off": ms_on / ms_off},
+            "roofline": roofline(r),
+            "host_link": {"achieved": link_gbs, "unit": "GB/s", "peak_spec": 64.0 * world, "frac_of_spec": link_gbs / (64.0 * world),
+                          "per_rank": r["link_bytes_rank"] / (ms_on * 1e-3) / 1e9,
+                          "measured_h2d_memcpy_peak": 55.4, "fetched_bytes_per_step": r["link_bytes"],
+                          "note": "residual bytes of a step (all ranks) / event-timed duration of the step with compensation on (lower bound of the link rate)"},
+            "e2e": {"value": 1e3 / r["ms_e2e"], "unit": "tokens/s", "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"],
+                    "ms_per_step": r["ms_e2e"]},
+            "gpu_launches": (r["calls"] + r["exchanges"] * (1 if args.allreduce == "push" else 0)) * args.steps,
             "clocks": clocks,
         }
-        if ms_tuned is not None:
-            tb = n_layers * sum(fetch_bytes(p["n"], p["k"], tuned_cfg["k_chunk"][p["name"]]) for p in model[0])
-            line["tuned"] = {"value": 1e3 / ms_tuned, "unit": "tokens/s", "ms_per_step": ms_tuned,
-                             "slowdown_vs_off": ms_tuned / ms_off, "n_tb": tuned_cfg["n_tb"], "k_chunk": tuned_cfg["k_chunk"],
-                             "fetched_bytes_per_step": tb,
+        if world > 1:
+            line["exchange"] = summary(r)["exchange"]
+        if "tuned" in r:
+            t = r["tuned"]
+            line["tuned"] = {"value": 1e3 / t["ms"], "unit": "tokens/s", "ms_per_step": t["ms"], "slowdown_vs_off": t["ms"] / ms_off,
+                             "n_tb": t["n_tb"], "k_chunk": t["k_chunk"], "fetched_bytes_per_step": t["bytes"],
                              "note": "operating point of the (n_tb, k_chunk) tuner for a 5 % layer slowdown budget"}
-        if ms_res is not None:
-            line["residual_in_hbm"] = {"value": 1e3 / ms_res, "unit": "tokens/s", "ms_per_step": ms_res, "slowdown_vs_off": ms_res / ms_off,
-                                       "k_chunk": args.k_chunk, "n_tb": args.resident_n_tb, "hbm_bytes_for_residual": int(link_bytes / args.k_chunk * 1024) if args.k_chunk else 0,
+        if "resident" in r:
+            t = r["resident"]
+            line["residual_in_hbm"] = {"value": 1e3 / t["ms"], "unit": "tokens/s", "ms_per_step": t["ms"], "slowdown_vs_off": t["ms"] / ms_off,
+                                       "k_chunk": args.k_chunk, "n_tb": t["n_tb"],
+                                       "hbm_bytes_for_residual": int(r["link_bytes"] / args.k_chunk * 1024) if args.k_chunk else 0,
                                        "note": "same launches with q_residual in device memory (create_dec_config accepts a CUDA tensor); not the reference's operating mode"}
-        if cpu:
-            line["cpu_baseline"] = cpu
+        if c4 is not None:
+            line["config4"] = c4 if "unavailable" in c4 else dict(summary(c4), workload=workload_config(args, "llama3-70b")["workload"])
+        if not args.no_cpu_baseline:
+            cb = cpu_baseline(args.model, args.k_chunk, 10, 1)
+            line["cpu_baseline"] = {"value": 1.0 / cb["s_per_token_dequant_every_call"], "unit": "tokens/s", "cores": cb["cores"], "kind": "port",
+                                    "sample": cb["sample"], "predequantised_tokens_per_s": 1.0 / cb["s_per_token_predequantised"]}
         print(json.dumps(line), flush=True)
     if dist is not None and args.allreduce == "push":
         allreduce.check()          # raises if any wait for a peer ever ran out
     if dist is not None:
         # graphs that captured NCCL work must go before the communicator; leave without running
         # interpreter-exit destructors, which can block on a communicator with captured collectives
-        graphs.clear()
         torch.cuda.synchronize()
         dist.barrier()
         sys.stdout.flush()

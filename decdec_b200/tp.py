@@ -8,7 +8,8 @@ per-layer tensors are cut so that the same kernels run unchanged on every rank:
       is q_residual[:, n0/8:n1/8]; `reordered_scales` is re-derived per shard because its layout
       [nibble][N_local/8] depends on the shard width (decdec_extension/dec.cu:223-224).
   row-parallel (o, down): inputs K are split at multiples of the 1024-channel selection chunk
-      (decdec_extension/macros.h:8) so that chunk-local selection equals the single-GPU selection.
+      (decdec_extension/macros.h:8) so that chunk-local selection equals the single-GPU selection; with
+      fewer chunks than ranks the ranks that share a chunk split its outputs (`row_plan`).
       Only thresholds[0] and thresholds[k-1] are read by the kernel (decdec_extension/decdec.cu:66-67),
       so a shard keeps the global bucket bounds by carrying those two values at [0] and [k_local-1].
       Partial outputs are summed with one all-reduce of [N] values.
@@ -41,13 +42,33 @@ def split_even(total: int, world: int, unit: int) -> List[Tuple[int, int]]:
     return out
 
 
+def row_plan(K: int, N: int, world: int) -> List[Tuple[int, int, int, int]]:
+    """Row-parallel plan: (k0, k1, n0, n1) per rank.  The input range of a rank is a whole number of
+    1024-channel selection chunks, so that chunk-local selection equals the single-GPU selection.
+      * K has at least `world` chunks: the chunks are dealt out as evenly as they go (28 chunks over 8 ranks:
+        4,4,4,4,3,3,3,3) and every rank produces all N outputs;
+      * fewer chunks than ranks: every chunk is shared by world / chunks ranks, which split its OUTPUTS
+        (a rank computes the partial sums of its output range over its chunk); world must be a multiple of
+        the chunk count.
+    In both cases the partial outputs, written into a zeroed [N] vector, are summed by one all-reduce.
+    A shard narrower than one chunk would select other channels than the unsharded layer
+    (decdec_extension/dec.cu:84-86 applies the quota per chunk), so it is refused."""
+    if K % CHUNK:
+        raise ValueError(f"row-parallel sharding needs in_features to be a multiple of {CHUNK} (got {K}): a partial chunk "
+                         "cannot be cut without changing the channel selection")
+    chunks = K // CHUNK
+    if chunks >= world:
+        return [(k0, k1, 0, N) for k0, k1 in split_even(K, world, CHUNK)]
+    if world % chunks:
+        raise ValueError(f"{chunks} selection chunks cannot be shared evenly by {world} ranks")
+    per = world // chunks
+    n_ranges = split_even(N, per, 128 if N % (128 * per) == 0 else 32)
+    return [(c * CHUNK, (c + 1) * CHUNK, *n_ranges[i]) for c in range(chunks) for i in range(per)]
+
+
 def k_ranges(K: int, world: int, group: int = 128) -> List[Tuple[int, int]]:
-    """Row-parallel input ranges: chunk-aligned when K has at least `world` chunks, else aligned to the
-    larger of 32 (one packed word) and the scale group, with the partial-chunk selection rule applied
-    inside each shard (decdec_extension/dec.cu:84-86)."""
-    if K % CHUNK == 0 and K // CHUNK >= world:
-        return split_even(K, world, CHUNK)
-    return split_even(K, world, max(32, group))
+    """Input ranges of `row_plan` (outputs ignored)."""
+    return [(k0, k1) for k0, k1, _, _ in row_plan(K, 32 * world, world)]
 
 
 def unreorder_scales(reordered: torch.Tensor) -> torch.Tensor:
@@ -71,15 +92,21 @@ def shard_residual(q_residual: torch.Tensor, reordered_scales: torch.Tensor, thr
                 "thresholds": thresholds.clone(), "k_chunk": k_chunk}
     if mode != "row":
         raise ValueError(mode)
-    k0, k1 = k_ranges(K, world, group)[rank]
+    k0, k1, n0, n1 = row_plan(K, N, world)[rank]
     k_glob = k_chunk * K // CHUNK
     k_loc = k_chunk * (k1 - k0) // CHUNK
     thr = thresholds[k0:k1].clone()
     if k_glob > 0 and k_loc > 0:
+        if k_loc == 1 and k_glob > 1:
+            raise ValueError("a shard that selects a single channel cannot carry both global bucket bounds (the kernel reads "
+                             "thresholds[0] and thresholds[k-1]); use k_chunk >= 2 or fewer ranks")
         thr[0] = thresholds[0]
         thr[k_loc - 1] = thresholds[k_glob - 1]
-    return {"q_residual": q_residual[k0:k1].contiguous(), "reordered_scales": reordered_scales.clone(),
-            "thresholds": thr, "k_chunk": k_chunk}
+    scales = reordered_scales.clone()
+    if (n0, n1) != (0, N):
+        scales = reorder_scales(unreorder_scales(reordered_scales)[n0:n1])
+    return {"q_residual": q_residual[k0:k1, n0 // 8:n1 // 8].contiguous(), "reordered_scales": scales,
+            "thresholds": thr, "k_chunk": k_chunk, "n_range": (n0, n1)}
 
 
 def shard_bcq(qweight: torch.Tensor, alpha: torch.Tensor, q_bias: torch.Tensor, group: int, mode: str, rank: int,
@@ -90,9 +117,9 @@ def shard_bcq(qweight: torch.Tensor, alpha: torch.Tensor, q_bias: torch.Tensor, 
         n0, n1 = split_even(N, world, 32)[rank]
         return {"qweight": qweight[:, :, n0:n1].contiguous(), "alpha": alpha[:, :, n0:n1].contiguous(),
                 "q_bias": q_bias[:, n0:n1].contiguous()}
-    k0, k1 = k_ranges(K, world, group)[rank]
-    return {"qweight": qweight[k0 // 32:k1 // 32].contiguous(), "alpha": alpha[k0 // group:k1 // group].contiguous(),
-            "q_bias": q_bias[k0 // group:k1 // group].contiguous()}
+    k0, k1, n0, n1 = row_plan(K, N, world)[rank]
+    return {"qweight": qweight[k0 // 32:k1 // 32, :, n0:n1].contiguous(), "alpha": alpha[k0 // group:k1 // group, :, n0:n1].contiguous(),
+            "q_bias": q_bias[k0 // group:k1 // group, n0:n1].contiguous(), "n_range": (n0, n1)}
 
 
 def shard_anyprec(qweight: torch.Tensor, lut: torch.Tensor, mode: str, rank: int, world: int) -> Dict[str, torch.Tensor]:
@@ -103,8 +130,8 @@ def shard_anyprec(qweight: torch.Tensor, lut: torch.Tensor, mode: str, rank: int
     if mode == "col":
         n0, n1 = split_even(N, world, 32)[rank]
         return {"qweight": qweight[:, n0:n1].contiguous(), "lut": lut[n0:n1].contiguous()}
-    k0, k1 = split_even(K, world, CHUNK)[rank]
-    return {"qweight": qweight[:, :, k0 // 32:k1 // 32].contiguous(), "lut": lut}
+    k0, k1, n0, n1 = row_plan(K, N, world)[rank]
+    return {"qweight": qweight[:, n0:n1, k0 // 32:k1 // 32].contiguous(), "lut": lut[n0:n1].contiguous(), "n_range": (n0, n1)}
 
 
 def shard_input(x: torch.Tensor, mode: str, rank: int, world: int, group: int = 128) -> torch.Tensor:

@@ -94,6 +94,10 @@ def test_bench_accounting():
     assert bench.gemv_bytes(4096, 4096) == pytest.approx(7.36e6, rel=0.01)        # table of algorithmic bytes: 7.36 MB
     assert bench.fetch_bytes(4096, 4096, 32) == 128 * 2048
     p = bench.projections("llama3-8b")
-    assert [(n, k) for _, n, k, _ in p] == [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]
+    assert [(e["n"], e["k"]) for e in p] == [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]
     p8 = bench.projections("llama3-70b", tp=8)
-    assert [(n, k) for _, n, k, _ in p8] == [(1280, 8192), (8192, 1024), (7168, 8192), (8192, 4096)]   # 28 chunks -> 4,4,4,4,3,3,3,3
+    assert [(e["n"], e["k"]) for e in p8] == [(1280, 8192), (8192, 1024), (7168, 8192), (8192, 4096)]   # 28 chunks -> 4,4,4,4,3,3,3,3
+    # Llama-3-8B over 8 ranks: wo has 4 selection chunks, so two ranks share a chunk and split its outputs
+    q8 = bench.projections("llama3-8b", tp=8, rank=3)
+    assert (q8[1]["n"], q8[1]["k"], q8[1]["n0"], q8[1]["n_full"]) == (2048, 1024, 2048, 4096)
+    assert (q8[3]["n"], q8[3]["k"]) == (4096, 2048)          # 14 chunks -> 2,2,2,2,2,2,1,1

@@ -2,17 +2,19 @@
 //
 // After a row-parallel GEMV every rank holds a partial output [N]; the sum has to reach every rank.  At
 // N = 4096-8192 that is 8-16 KB: a latency problem, not a bandwidth problem.  One kernel per rank:
-//   1. push   : the rank stores its partial vector into a slot of every peer's buffer (plain 16-byte
-//               stores to peer-mapped memory, NVLink), fences at system scope and then raises a flag
-//               per (source rank, thread block) in the peer's buffer (release, system scope);
-//   2. wait   : each thread block polls the flags of its own slice from every peer (acquire, system
-//               scope).  The wait is bounded; on expiry the block records an error and leaves y as is;
-//   3. reduce : the block sums the world's slices in rank order in fp32 (identical on every rank) and
+//   1. push   : the rank stores its partial vector into a slot of every peer's buffer over NVLink.  The
+//               slot is made of 16-byte lines {data, flag, data, flag}: every 8-byte half carries the call
+//               number next to its 4 bytes of payload, so a line validates itself wherever the fabric
+//               splits it - no fence and no separate flag after the data;
+//   2. wait   : each thread polls the lines of its own 16 bytes of output from every peer until both flags
+//               show this call.  The wait is bounded; on expiry the block records an error and leaves y as is;
+//   3. reduce : the thread sums the world's values in rank order in fp32 (identical on every rank) and
 //               writes y.
 // Slots alternate between two halves by call parity: a peer can be at most one call ahead (it needs
-// this rank's flags of call e to finish e), so half (e & 1) is never overwritten while it is still
-// being read.  The call counter lives in device memory and is advanced by the kernel itself, which
-// makes the call replayable inside CUDA graphs.  No multicast, no multimem: plain peer stores.
+// this rank's lines of call e to finish e), so half (e & 1) is never overwritten while it is still
+// being read, and what an older call left there carries an older flag.  The call number lives in device
+// memory, one counter per thread block of the (fixed) grid, advanced by the kernel itself, which makes the
+// call replayable inside CUDA graphs.  No multicast, no multimem: plain peer stores and local polls.
 // The reference has no tensor parallelism; this file has no counterpart there.
 #include "internal.h"
 #include "../../include/decdec_b200.h"
@@ -37,9 +39,9 @@ struct TpLayout {
 
 TpLayout tp_layout(uint32_t world, uint32_t max_n) {
     TpLayout L;
-    L.flags_off = kTpHdr;
+    L.flags_off = kTpHdr;                                          // call counters, one per thread block of the grid
     L.slots_off = (L.flags_off + (size_t)world * kTpMaxCta * sizeof(uint32_t) + 255) & ~(size_t)255;
-    L.slot_stride = (uint32_t)(((size_t)max_n * 4 + 255) & ~(size_t)255);
+    L.slot_stride = (uint32_t)(((size_t)max_n * 8 + 255) & ~(size_t)255);     // 8 bytes of line per 4 bytes of payload (fp32 worst case)
     L.bytes = L.slots_off + 2 * (size_t)world * L.slot_stride;
     return L;
 }
@@ -52,6 +54,7 @@ struct TpComm {
     bool opened[kTpMaxWorld];        // peers[i] came from cudaIpcOpenMemHandle
     bool connected;
     uint32_t wait_polls;
+    uint32_t grid;                   // thread blocks of every launch: enough for max_n fp32 values
     TpLayout L;
 };
 
@@ -62,97 +65,83 @@ struct TpArgs {
     uint32_t wait_polls;
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_line(unsigned char* p, uint32_t d0, uint32_t d1, uint32_t flag) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" :: "l"(p), "r"(d0), "r"(flag), "r"(d1), "r"(flag) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_line(const unsigned char* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
 
+// A thread owns 16 bytes of y = four 32-bit payload words = two lines of a slot.
 template <int DT>
 __global__ void __launch_bounds__(kTpThreads) k_tp_allreduce(const __grid_constant__ TpArgs a, void* y_) {
     using T = typename Tr<DT>::T;
     constexpr uint32_t EPT = 16 / sizeof(T);                       // elements per 16-byte vector
-    __shared__ uint32_t s_epoch, s_bad;
+    __shared__ uint32_t s_bad;
     pdl_trigger();                 // the next kernel of the stream may become resident while this one exchanges
-    pdl_wait();                    // y comes from the previous kernel
     unsigned char* mine = a.peers[a.rank];
     uint32_t* hdr = reinterpret_cast<uint32_t*>(mine);
-    if (threadIdx.x == 0) {
-        s_epoch = *reinterpret_cast<volatile uint32_t*>(hdr) + 1u;
-        s_bad = 0u;
-    }
-    __syncthreads();
-    const uint32_t e = s_epoch, half = e & 1u;
-    const uint32_t idx = (blockIdx.x * kTpThreads + threadIdx.x) * EPT;      // first element of this thread
+    uint32_t* counter = reinterpret_cast<uint32_t*>(mine + a.flags_off) + blockIdx.x;
+    if (threadIdx.x == 0) s_bad = 0u;
+    pdl_wait();                    // y comes from the previous kernel; so does this block's call counter
+    const uint32_t e = *reinterpret_cast<volatile uint32_t*>(counter) + 1u, half = e & 1u;
+    __syncthreads();               // everybody has read the counter before thread 0 advances it
+    const uint32_t vec = blockIdx.x * kTpThreads + threadIdx.x;              // index of this thread's 16 bytes
+    const uint32_t idx = vec * EPT;
     const bool act = idx < a.n;
     T* y = reinterpret_cast<T*>(y_);
     uint4 v = make_uint4(0, 0, 0, 0);
     if (act) v = *reinterpret_cast<const uint4*>(y + idx);
 
-    // 1. push
-    const size_t my_slot = (size_t)a.slots_off + ((size_t)half * a.world + a.rank) * a.slot_stride + (size_t)idx * sizeof(T);
+    // 1. push: two self-validating lines per peer
+    const size_t line0 = (size_t)a.slots_off + ((size_t)half * a.world + a.rank) * a.slot_stride + (size_t)vec * 32u;
     if (act)
         for (uint32_t s = 0; s < a.world; ++s)
-            if (s != a.rank) *reinterpret_cast<uint4*>(a.peers[s] + my_slot) = v;
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x < a.world && threadIdx.x != a.rank) {
-        uint32_t* flag = reinterpret_cast<uint32_t*>(a.peers[threadIdx.x] + a.flags_off) + a.rank * kTpMaxCta + blockIdx.x;
-        st_release_sys(flag, e);
-    }
+            if (s != a.rank) {
+                st_line(a.peers[s] + line0, v.x, v.y, e);
+                st_line(a.peers[s] + line0 + 16, v.z, v.w, e);
+            }
 
-    // 2. wait (bounded)
-    if (threadIdx.x < a.world && threadIdx.x != a.rank) {
-        const uint32_t* flag = reinterpret_cast<const uint32_t*>(mine + a.flags_off) + threadIdx.x * kTpMaxCta + blockIdx.x;
-        uint32_t polls = 0;
-        // flags only grow; a peer that is one call ahead shows e + 1
-        uint32_t seen;
-        while ((int32_t)((seen = ld_acquire_sys(flag)) - e) < 0) {
-            if (++polls >= a.wait_polls) { atomicExch(&s_bad, 1u); break; }
-            __nanosleep(64);
-        }
-        // two or more calls ahead can only happen after this rank missed a bounded wait of the peer: the
-        // slot of this parity may already hold a later vector, so the sum is not formed
-        if ((int32_t)(seen - e) >= 2) atomicExch(&s_bad, 1u);
-    }
-    __syncthreads();
-
-    // 3. reduce in rank order
-    if (s_bad) {
-        if (threadIdx.x == 0) atomicExch(hdr + 2, 1u);
-    } else if (act) {
-        float acc[EPT];
+    // 2. wait (bounded) and 3. reduce in rank order
+    float acc[EPT];
 #pragma unroll
-        for (uint32_t i = 0; i < EPT; ++i) acc[i] = 0.0f;
-        for (uint32_t s = 0; s < a.world; ++s) {
+    for (uint32_t i = 0; i < EPT; ++i) acc[i] = 0.0f;
+    if (act) {
+        bool bad = false;
+        for (uint32_t s = 0; s < a.world && !bad; ++s) {
             uint4 q = v;
             if (s != a.rank) {
-                const size_t off = (size_t)a.slots_off + ((size_t)half * a.world + s) * a.slot_stride + (size_t)idx * sizeof(T);
-                q = __ldcg(reinterpret_cast<const uint4*>(mine + off));
+                const unsigned char* src = mine + (size_t)a.slots_off + ((size_t)half * a.world + s) * a.slot_stride + (size_t)vec * 32u;
+                uint4 l0 = ld_line(src), l1 = ld_line(src + 16);
+                uint32_t polls = 0;
+                while (l0.y != e || l0.w != e || l1.y != e || l1.w != e) {
+                    if (++polls >= a.wait_polls) { bad = true; break; }
+                    __nanosleep(32);
+                    l0 = ld_line(src);
+                    l1 = ld_line(src + 16);
+                }
+                q = make_uint4(l0.x, l0.z, l1.x, l1.z);
             }
             const T* e4 = reinterpret_cast<const T*>(&q);
 #pragma unroll
             for (uint32_t i = 0; i < EPT; ++i) acc[i] += Tr<DT>::to_f(e4[i]);
         }
+        if (bad) atomicExch(&s_bad, 1u);
+    }
+    __syncthreads();
+    if (act && !s_bad) {           // if any wait of the block ran out, the block leaves its part of y as it was
         uint4 o;
         T* o4 = reinterpret_cast<T*>(&o);
 #pragma unroll
         for (uint32_t i = 0; i < EPT; ++i) o4[i] = Tr<DT>::from_f(acc[i]);
         *reinterpret_cast<uint4*>(y + idx) = o;
     }
-
-    // the block that leaves last advances the call counter
-    __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence();
-        if (atomicAdd(hdr + 1, 1u) + 1u == gridDim.x) {
-            hdr[1] = 0u;
-            __threadfence();
-            *reinterpret_cast<volatile uint32_t*>(hdr) = e;
-        }
+        if (s_bad) atomicExch(hdr + 2, 1u);
+        *reinterpret_cast<volatile uint32_t*>(counter) = e;
+        if (blockIdx.x == 0) *reinterpret_cast<volatile uint32_t*>(hdr) = e;     // calls completed, read by decdec_tp_status
     }
 }
 
@@ -184,6 +173,7 @@ int decdec_tp_create(uint32_t world, uint32_t rank, uint32_t max_n, uintptr_t* c
     memset(c, 0, sizeof(*c));
     c->world = world; c->rank = rank; c->max_n = max_n;
     c->L = tp_layout(world, max_n);
+    c->grid = (max_n + kTpThreads * 4u - 1) / (kTpThreads * 4u);       // every launch has this many blocks, so their call counters stay in step
     const char* wp = getenv("DECDEC_TP_WAIT_POLLS");
     c->wait_polls = (wp && *wp) ? (uint32_t)strtoul(wp, nullptr, 10) : (1u << 21);     // about a second
     if (c->wait_polls == 0) c->wait_polls = 1;
@@ -261,8 +251,7 @@ int decdec_tp_allreduce(uintptr_t comm, void* y_dev, uint32_t n, int dtype, void
     a.world = c->world; a.rank = c->rank; a.n = n;
     a.flags_off = (uint32_t)c->L.flags_off; a.slots_off = (uint32_t)c->L.slots_off; a.slot_stride = c->L.slot_stride;
     a.wait_polls = c->wait_polls;
-    const uint32_t grid = (n + kTpThreads * ept - 1) / (kTpThreads * ept);
-    if (grid > kTpMaxCta) return tp_fail(DECDEC_E_UNSUPPORTED, "tp: vector too long for the flag table");
+    const uint32_t grid = c->grid;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     // programmatic dependent launch: the blocks become resident while the GEMV before them drains
     cudaLaunchConfig_t cfg = {};

@@ -134,8 +134,9 @@ int decdec_lutgemm_dequant(const int32_t* qweight, const void* alpha, const void
 
 /* ---- tensor-parallel output exchange.  NO COUNTERPART IN THE REFERENCE (it has no tensor parallelism). -------
  * One-shot push all-reduce of the [n] partial outputs of a row-parallel projection over NVLink peer memory:
- * every rank stores its vector into every peer's buffer, raises a flag, waits (bounded) for the peers'
- * flags and sums in rank order, in one kernel per rank.  Replaces ncclAllReduce for these 8-16 KB vectors.
+ * every rank stores its vector into every peer's buffer as 16-byte lines that carry the call number beside the
+ * payload (no fence, no separate flag), waits (bounded) for the peers' lines and sums in rank order, in one
+ * kernel per rank.  Replaces ncclAllReduce for these 8-16 KB vectors.
  *
  *   decdec_tp_create       allocates this rank's exchange buffer on the current device; ipc_handle_out (64 bytes,
  *                          may be null) receives its cudaIpcMemHandle_t for the other processes.
@@ -144,9 +145,11 @@ int decdec_lutgemm_dequant(const int32_t* qweight, const void* alpha, const void
  *   decdec_tp_allreduce    y_dev[n] <- sum over ranks, in place, on `stream`.  All ranks must make the same
  *                          sequence of calls with the same n.  Capturable in a CUDA graph.  n <= max_n,
  *                          n*sizeof(dtype) a multiple of 16, y_dev 16-byte aligned.
- *   decdec_tp_status       calls completed and the error word (1 = a wait ran out: a peer did not arrive
- *                          within DECDEC_TP_WAIT_POLLS polls, default 2^21, about a second; y was left unsummed).
- *   decdec_tp_layout       byte offsets inside an exchange buffer (flags [world][64] u32, slots [2][world][stride]).
+ *   decdec_tp_status       calls completed and the error word (1 = a wait ran out: a peer's lines did not arrive
+ *                          within DECDEC_TP_WAIT_POLLS polls, default 2^21, about a second; that block's part of y was left unsummed).
+ *   decdec_tp_layout       byte offsets inside an exchange buffer (call counters [world][64] u32 of which the first
+ *                          row is used, slots [2][world][stride]; a slot is a sequence of lines {u32 payload, u32 call,
+ *                          u32 payload, u32 call}).
  */
 int decdec_tp_layout(uint32_t world, uint32_t max_n, size_t* flags_off, size_t* slots_off, size_t* slot_stride, size_t* bytes);
 int decdec_tp_create(uint32_t world, uint32_t rank, uint32_t max_n, uintptr_t* comm_out, unsigned char* ipc_handle_out);

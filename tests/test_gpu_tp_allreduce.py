@@ -1,7 +1,7 @@
 """Push all-reduce of the row-parallel outputs (decdec_tp_allreduce), through the C ABI.
 
-On one GPU the peer is emulated by staging what it would have pushed (its vector and its flags) into this
-rank's exchange buffer BEFORE the launch, so no kernel ever waits for another kernel on the same GPU.  The
+On one GPU the peer is emulated by staging what it would have pushed (its vector as self-validating lines
+{payload, call, payload, call}) into this rank's exchange buffer BEFORE the launch, so no kernel ever waits for another kernel on the same GPU.  The
 failure path is a wait that runs out (flags nobody sets) with a short limit; the kernel returns an error status
 and the context stays usable.  With two or more GPUs the real exchange runs as two processes and is compared
 with NCCL's all-reduce.
@@ -73,20 +73,23 @@ def test_staged_peers_sum_in_rank_order(capi, dtype, world, rank):
     table = (C.c_size_t * world)(*[(ptr if s == rank else peers[s].data_ptr()) for s in range(world)])
     capi.call("decdec_tp_connect_ptrs", comm, table)
     esz = torch.empty(0, dtype=dtype).element_size()
-    ept = 16 // esz
-    n_cta = -(-n // (256 * ept))
     g = torch.Generator(device="cuda").manual_seed(world * 10 + rank)
     stream = torch.cuda.current_stream().cuda_stream
+
+    def lines(vec, call):
+        """The slot image of a vector: payload words interleaved with the call number."""
+        words = vec.contiguous().view(torch.int32)
+        return torch.stack([words, torch.full_like(words, call)], dim=1).reshape(-1)
+
     for call in (1, 2, 3):
         half = call & 1
         vecs = [torch.randn(n, device="cuda", generator=g).to(dtype) for _ in range(world)]
+        nwords = n * esz // 4
         for s in range(world):
             if s == rank:
                 continue
             off = slots_off + (half * world + s) * stride
-            mine[off:off + n * esz].view(dtype).copy_(vecs[s])                     # what peer s would have pushed
-            fl = mine[flags_off:flags_off + world * 64 * 4].view(torch.int32).view(world, 64)
-            fl[s, :n_cta] = call                                                    # ... and its flags
+            mine[off:off + nwords * 8].view(torch.int32).copy_(lines(vecs[s], call))        # what peer s would have pushed
         y = vecs[rank].clone()
         torch.cuda.synchronize()
         capi.call("decdec_tp_allreduce", comm, y.data_ptr(), n, DT[dtype], stream)
@@ -96,12 +99,10 @@ def test_staged_peers_sum_in_rank_order(capi, dtype, world, rank):
             acc += vecs[s].float()
         assert torch.equal(y, acc.to(dtype)), f"call {call}: sum differs"
         assert _status(capi, comm) == (call, 0)
-        # this rank's vector and flags arrived in every peer's buffer
+        # this rank's lines arrived in every peer's buffer, in its own slot of this call's half
         for s, buf in peers.items():
             off = slots_off + (half * world + rank) * stride
-            assert torch.equal(buf[off:off + n * esz].view(dtype), vecs[rank])
-            fl = buf[flags_off:flags_off + world * 64 * 4].view(torch.int32).view(world, 64)
-            assert (fl[rank, :n_cta] == call).all() and (fl[rank, n_cta:] == 0).all()
+            assert torch.equal(buf[off:off + nwords * 8].view(torch.int32), lines(vecs[rank], call))
     capi.call("decdec_tp_destroy", comm)
 
 
@@ -174,7 +175,7 @@ def _rank_main(rank, world, port, q):
         torch.cuda.synchronize()
         ok &= _same(y, ref)
         # every rank sums in rank order: the result is bit-identical on all of them
-        mine = y.view(torch.int16).clone()
+        mine = y.view(torch.int32).clone()      # two fp16 values per word (NCCL has no 16-bit integer type)
         lo, hi = mine.clone(), mine.clone()
         dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)

@@ -469,7 +469,7 @@ def run_micro(args):
     """One entry point on one layer shape: `--micro KIND --n N --k K [--k-chunk C --n-tb T --iters I]`.
     Launches rotate over enough distinct weight tensors to exceed L2 (cache-cold), are captured in a CUDA
     graph and timed with CUDA events; prints one JSON line (us per launch, algorithmic GB/s).  Also the
-    command used for the single-kernel ncu captures under profiles/."""
+    command used for single-kernel ncu captures."""
     import torch
     import decdec_ext as ext
     dev = torch.device("cuda", 0)

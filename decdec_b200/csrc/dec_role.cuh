@@ -20,20 +20,6 @@
 
 namespace dd {
 
-#ifdef DD_PROF
-// debug builds only: per-CTA phase time stamps (ns)
-__device__ unsigned long long g_dd_prof[512 * 8];
-__device__ __forceinline__ void dd_stamp(uint32_t cta, int slot) {
-    if (threadIdx.x == 0 && cta < 512) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        g_dd_prof[cta * 8 + slot] = t;
-    }
-}
-#define DD_STAMP(cta, slot) dd_stamp(cta, slot)
-#else
-#define DD_STAMP(cta, slot)
-#endif
 
 // Barrier of the first kThreads threads of the CTA (selection and the grouped fetch run on those; a launch
 // shared with a wider GEMV role has more threads, which only join the CTA-wide phases).
@@ -283,13 +269,11 @@ __device__ void dec_fetch(const DecParams& p, float* acc_g, uint32_t nrows, uint
                 }
             }
         }
-        DD_STAMP(blockIdx.x, 4);
         // per-thread partials -> red[value][thread] (pitch 257: conflict-free both ways), then each
         // output sums its R row groups
 #pragma unroll
         for (int i = 0; i < VW * 8; ++i) red[i * 257 + tid] = a[i];
         dec_bar();
-        DD_STAMP(blockIdx.x, 5);
         for (uint32_t o = tid; o < nw * 8; o += kThreads) {
             const uint32_t vv = o / (VW * 8), i = o % (VW * 8);
             float sum = 0.0f;
@@ -297,7 +281,6 @@ __device__ void dec_fetch(const DecParams& p, float* acc_g, uint32_t nrows, uint
             atomicAdd(&acc_g[cb * 8 + o], sum);      // unscaled: the scale is applied when the tile is finalized
         }
         dec_bar();
-        DD_STAMP(blockIdx.x, 6);
     }
 }
 
@@ -385,7 +368,6 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
     const bool direct = vec && ((w1 - w0) * 4u >= nthr || ((w1 - w0) * 8u >= nthr && p.k_chunk <= 16u));
     int* srow = reinterpret_cast<int*>(sm + DecSmem::kRow);
     float* sact = reinterpret_cast<float*>(sm + DecSmem::kAct);
-    DD_STAMP(cta, 0);
 
     if (p.fused_select) {
         const uint32_t num_chunks = (p.K + kChunk - 1) / kChunk;
@@ -395,7 +377,6 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
             if (kq == 0) continue;
             if (first) dec_select_chunk<DT>(p, c, kq, cp == 0, sm);
             __syncthreads();
-            DD_STAMP(cta, 1);
             if (w1 > w0) {
                 if (direct) dec_fetch_direct<DT>(p, f.acc2, kq, w0, w1, sm, nthr);
                 else if (first) {
@@ -429,9 +410,7 @@ __device__ void dec_role(const DecParams& p, const FinParams& f, uint32_t cta, u
             __syncthreads();
         }
     }
-    DD_STAMP(cta, 2);
     arrive_and_finalize<DT>(f, t0, t1, reinterpret_cast<unsigned*>(sm + DecSmem::kFlag), nthr);
-    DD_STAMP(cta, 3);
 }
 
 // ---- compensation role of launches without tickets (packed accumulator words, common.cuh) -------------------------
@@ -516,7 +495,6 @@ __device__ void dec_role_packed(const DecParams& p, const FinParams& f, uint32_t
     float* cells = reinterpret_cast<float*>(sm + kDecPrivOff);
     for (uint32_t i = threadIdx.x; i < 32u * stride; i += nthr) cells[i] = 0.0f;
     pdl_wait();                             // everything below reads activations / writes shared state
-    DD_STAMP(cta, 0);
     const uint32_t num_chunks = (p.K + kChunk - 1) / kChunk;
     for (uint32_t c = rp; c < num_chunks; c += p.n_rowparts) {
         const uint32_t len = min((uint32_t)kChunk, p.K - c * kChunk);
@@ -524,12 +502,10 @@ __device__ void dec_role_packed(const DecParams& p, const FinParams& f, uint32_t
         if (kq == 0) continue;
         if (first) dec_select_chunk<DT>(p, c, kq, cp == 0, sm);
         __syncthreads();
-        DD_STAMP(cta, 1);
         if (nvec) dec_fetch_private<DT>(p, cells, nslots, stride, kq, w0, nvec, sm, nthr);
         __syncthreads();                // the next chunk's selection overwrites srow/sact
     }
     __syncthreads();
-    DD_STAMP(cta, 2);
     // one arrival per output of the column range; lanes take CONSECUTIVE outputs, so the accesses to y, to the
     // accumulator words and (four lanes per sector) to the scales coalesce
     const uint32_t R = nthr / max(nvec, 1u);
@@ -564,7 +540,6 @@ __device__ void dec_role_packed(const DecParams& p, const FinParams& f, uint32_t
         for (int u = 0; u < U; ++u)
             if (nn[u] != 0xffffffffu) finish_packed<DT>(old[u], mine[u], arrivals, words + nn[u], y + nn[u], y0[u]);
     }
-    DD_STAMP(cta, 3);
 }
 
 }  // namespace dd

@@ -37,7 +37,7 @@
 #include "common.cuh"
 #include "gemv_bcq.cuh"
 #include <cuda.h>
-#include "dec_role.cuh"   // DD_STAMP (debug builds)
+#include "dec_role.cuh"
 
 namespace dd {
 
@@ -186,7 +186,6 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     pdl_trigger();
-    DD_STAMP(cta + 256, 0);
     const uint32_t ks = cta % p.n_kslices;
     const uint32_t tile = cta / p.n_kslices;
     const uint32_t kbase = ks * kBcqSlice;
@@ -284,7 +283,6 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
         float p_y0 = 0.0f;
 
         pdl_wait();     // weights are already streaming (producer warp); activations come from earlier kernels
-        DD_STAMP(cta + 256, 5);
         if (builder && !*s_abort) {
             float xv[8];
             pipe_load_x8<DT>(p.x, kbase + koff, xvec, xv);
@@ -308,13 +306,11 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
             if (qe == 0 && (lane & 3) == 0) rowsum[krow_b] = rs;
         }
         asm volatile("bar.sync 1, %0;" ::"n"(NCONS) : "memory");
-        DD_STAMP(cta + 256, 1);
         const float sx = rowsum[krow];
 
         for (uint32_t i = grp; i < nst && !*s_abort; i += kPipeGroups) {
             const uint32_t s = i % S;
             if (!mbar_wait(bar_full + 8 * s, (i / S) & 1u, s_abort, geo.wait_ns)) break;
-            if (i == 0) DD_STAMP(cta + 256, 2);
             const unsigned char* st = stage_ptr(s);
             const unsigned char* wl = st + krow * (BITS * kPipeLine);
             const unsigned char* al = st + geo.w_bytes + (g * BITS) * (kPipeStageN * ESZ);
@@ -380,13 +376,11 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
         }
         if (pending) finish_packed<DT>(p_old, p_mine, geo.arrivals, p_word, p_y, p_y0);
     }
-    DD_STAMP(cta + 256, 3);
     if (geo.packed) {
         // nothing to hand over: every output was settled by the lane that made its last arrival.  A wait that ran out
         // leaves the words of the unfinished outputs dirty (their y untouched) until decdec_stream_reset.
         __syncthreads();
         if (*s_abort && tid == 0) raise_error(f.err, *s_abort);
-        DD_STAMP(cta + 256, 4);
         return;
     }
     // Fused launch: whatever happened above, the CTA takes a ticket on its tile, so that accumulator and tickets are
@@ -394,7 +388,6 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
     __syncthreads();
     if (*s_abort && tid == 0) raise_error(f.err, *s_abort);
     arrive_and_finalize<DT>(f, tile, tile + 1, s_flag, kPipeThreads);
-    DD_STAMP(cta + 256, 4);
 }
 
 }  // namespace dd

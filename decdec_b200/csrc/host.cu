@@ -463,16 +463,6 @@ int decdec_stream_status(void* stream, uint32_t* error_out) {
     return 0;
 }
 
-#ifdef DD_BEACON
-int decdec_debug_beacon(void* stream, uint32_t* out16) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    auto it = g_ws.find({dev, reinterpret_cast<cudaStream_t>(stream)});
-    if (it == g_ws.end()) return -1;
-    for (int i = 0; i < 16; ++i) out16[i] = it->second.err_host[i];
-    return 0;
-}
-#endif
 
 int decdec_stream_reset(void* stream) {
     int dev = 0;

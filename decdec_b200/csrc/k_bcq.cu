@@ -202,8 +202,3 @@ cudaError_t launch_bcq_dequant(int dt, const uint32_t* qweight, const void* alph
 }
 
 }  // namespace dd
-#ifdef DD_PROF
-extern "C" int decdec_debug_prof_bcq(unsigned long long* out, int n) {
-    return (int)cudaMemcpyFromSymbol(out, dd::g_dd_prof, sizeof(unsigned long long) * n);
-}
-#endif

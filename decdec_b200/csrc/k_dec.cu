@@ -47,10 +47,5 @@ cudaError_t launch_burner(int blocks, long long iters, cudaStream_t s) {
     return cudaGetLastError();
 }
 
-#ifdef DD_PROF
-extern "C" int decdec_debug_prof(unsigned long long* out, int n) {
-    return (int)cudaMemcpyFromSymbol(out, g_dd_prof, sizeof(unsigned long long) * n);
-}
-#endif
 
 }  // namespace dd

@@ -49,7 +49,7 @@ def _ctx(ops, n_tb, size, dtype):
 # ------------------------------------------------------------------------------------------------
 
 def test_lutgemm_config0_fp16(ops):
-    """BASELINE config 0: 4096x4096, 3-bit asymmetric group-128, fp16; output accumulated into y0."""
+    """The single-layer configuration: 4096x4096, 3-bit asymmetric group-128, fp16; output accumulated into y0."""
     N = K = 4096
     L = P.bcq_layer(N, K, 3, 128, seed=1)
     x = P.make_activation(K, seed=2)
@@ -267,7 +267,7 @@ def test_k_chunk_zero_is_noop_and_update(ops):
 # ------------------------------------------------------------------------------------------------
 
 def test_dec_lutgemm_config0(ops):
-    """BASELINE config 0 end to end: real 3-bit quantization, real 4-bit residual, k_chunk = 32."""
+    """The single-layer configuration end to end: real 3-bit quantization, real 4-bit residual, k_chunk = 32."""
     N = K = 4096
     L = P.bcq_layer(N, K, 3, 128, seed=1)
     cs, rs = P.quantized_residual(L["w"], L["w_fake"])
@@ -379,7 +379,7 @@ def test_fused_projection_artifacts_feed_the_kernel(ops):
 
 @pytest.mark.parametrize("k_chunk", [0, 8, 16, 32, 64])
 def test_dec_anyprec_config1_sweep(ops, k_chunk):
-    """BASELINE config 1 (k/v projection shape 4096 -> 1024), 3-bit LUT, k_chunk sweep."""
+    """Llama-3-8B k/v projection shape (4096 -> 1024), 3-bit non-uniform LUT weights, k_chunk sweep."""
     N, K = 1024, 4096
     L = P.lut_layer(N, K, 3, seed=41)
     cs, rs = P.random_residual(N, K, seed=42)
@@ -396,7 +396,7 @@ def test_dec_anyprec_config1_sweep(ops, k_chunk):
 
 @pytest.mark.parametrize("N,K,k_chunk,n_tb", [(14336, 4096, 64, 96), (14336, 4096, 8, 16), (4096, 14336, 16, 32), (4096, 4096, 32, 64)])
 def test_dec_anyprec_config1_full_shapes(ops, N, K, k_chunk, n_tb):
-    """BASELINE config 1 at the full Llama-3-8B projection sizes (gate/up, down, q/o), random 3-bit codes and LUTs."""
+    """3-bit LUT weights at the full Llama-3-8B projection sizes (gate/up, down, q/o), random codes and LUTs."""
     L = P.lut_layer(N, K, 3, seed=N + k_chunk, real=False)
     cs, rs = P.random_residual(N, K, seed=45)
     thr = P.make_thresholds(K)
@@ -411,10 +411,12 @@ def test_dec_anyprec_config1_full_shapes(ops, N, K, k_chunk, n_tb):
     assert np.array_equal(rows[:k].cpu().numpy(), exp_rows)
     delta = ofw.dec_delta(P.to_np(x), exp_rows, cs.numpy(), P.to_np(rs), exp_acts)
     ma, rl = P.errors(y, ofw.layer_output(L["w_hat"], P.to_np(x), None, delta))
-    # rel L2 as everywhere; the max-abs bound is 3e-2 here: the any-precision kernel adds 8 products in half2 before it
-    # goes to fp32 (the reference adds in half too), and with x20 outliers over up to 14336 channels single outputs of
-    # magnitude 10-30 land 1-2 fp16 ulps (0.008-0.016 each) from the float64 value
-    assert rl <= TOL["fp16"][1] and ma <= 3e-2, f"dec_anyprec {N}x{K} kc={k_chunk}: max abs {ma:.3e}, rel L2 {rl:.3e}"
+    # rel L2 as everywhere.  Max abs: the kernel adds 4 products per half lane in fp16 before it goes to fp32 (the reference
+    # adds whole rows in fp16); with x20 outliers over up to 14336 channels single outputs of magnitude 10-30 land one fp16
+    # ulp (0.008-0.016) from the float64 value.  Measured on the same inputs (test_gpu_reference_crosscheck.py): this kernel
+    # 0.6e-2 .. 1.3e-2, the reference's own kernel 1.5e-2 .. 2.8e-2 - so the bound here is 2e-2, not the 1e-2 of the
+    # fp32-accumulating kernels, and the cross-check asserts that this kernel is never worse than the reference.
+    assert rl <= TOL["fp16"][1] and ma <= 2e-2, f"dec_anyprec {N}x{K} kc={k_chunk}: max abs {ma:.3e}, rel L2 {rl:.3e}"
     ops.destroy_dec_config(cfg)
 
 

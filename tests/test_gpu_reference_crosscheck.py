@@ -14,7 +14,8 @@ tensors to that module and to this library (through the C ABI) and compare
     err(new, oracle) <= max(1e-2, err(ref, oracle)) (max abs) and rel L2 <= max(1e-3, ref's).
 
 The reference trips a device assert on activations that are not finite (dec.cu:178), so only finite
-inputs are given to it.  The measured table is written to gpurun_out/reference_crosscheck.json.
+inputs are given to it.  The measured table is written to reference_crosscheck.json in the directory that the
+environment variable DECDEC_REPORT_DIR names (if set).
 """
 import importlib.util
 import json
@@ -54,8 +55,8 @@ def ref():
     if mod is None:
         pytest.skip("reference build absent: run `python oracle/build_ref.py <DecDEC checkout>` first")
     yield mod
-    out = os.path.join(ROOT, "gpurun_out")
-    if REPORT and os.path.isdir(out):
+    out = os.environ.get("DECDEC_REPORT_DIR", "")
+    if REPORT and out and os.path.isdir(out):
         with open(os.path.join(out, "reference_crosscheck.json"), "w") as f:
             json.dump(REPORT, f, indent=1, sort_keys=True)
 

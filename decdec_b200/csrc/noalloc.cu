@@ -2,9 +2,9 @@
 //
 // The ordinary entry points keep their fp32 accumulator and tile tickets in a workspace that the
 // library obtains with cudaMalloc on first use of a (device, stream).  Some hosts cannot take that
-// path: code running between cudaStreamBeginCapture and EndCapture, real-time loops that forbid
-// calls which may synchronise the device or touch the driver's heap, and embedders whose device
-// memory is handed out up front by their own arena and who therefore ban cudaMalloc in plug-ins.
+// path: real-time loops that forbid calls which may synchronise the device or touch the driver's
+// heap, and embedders whose device memory is handed out up front by their own arena and who
+// therefore ban cudaMalloc in plug-ins.
 // For them this file carries the same scratch as a fixed array inside the library image.  The
 // array exists once per GPU that loads the library, for the life of the process, whether or not
 // this entry point is ever called; that is why it is kept modest (kMaxN outputs).

@@ -116,8 +116,8 @@ int decdec_sqllm_gemv(const void* x_dev, void* y_dev, const int32_t* qweight, co
  * Same arguments and result as decdec_lutgemm_gemv.  The accumulator workspace that the other entry
  * points obtain with cudaMalloc is replaced by a fixed array inside the library (held by every GPU
  * that loads the library until the process exits), so the call is usable by hosts that may not call
- * cudaMalloc at that point: plug-ins of an application that owns all device memory, real-time loops,
- * code that is already inside a stream capture.  Limits and duties of the caller:
+ * cudaMalloc at that point: plug-ins of an application that owns all device memory, and real-time loops
+ * that forbid calls which may synchronise the device.  Limits and duties of the caller:
  *   - out_features <= 32768, otherwise DECDEC_E_UNSUPPORTED;
  *   - the first call on a device resolves the array's address; make it before any stream capture;
  *   - all calls on one GPU share the array: calls that overlap in time on the GPU race. */

@@ -1,6 +1,5 @@
 """GPU test of `decdec_lutgemm_gemv_noalloc`, the entry point for hosts that may not allocate device
-memory at call time (an application that owns the whole device heap, a real-time loop, code inside a
-stream capture).  It keeps its accumulator in a fixed array inside the library instead of a
+memory at call time (an application that owns the whole device heap, a real-time loop).  It keeps its accumulator in a fixed array inside the library instead of a
 cudaMalloc'd workspace.  The test calls it through the C ABI twice in a row and checks both results
 against the regular `decdec_lutgemm_gemv` within the fp16 tolerance of the parity tests (max abs 1e-2,
 rel L2 1e-3 against the oracle; the two entry points themselves must agree to output rounding).

@@ -322,6 +322,8 @@ class Workload:
 
     def capture(self, key, mode):
         torch = self.env["torch"]
+        self.barrier()                       # ranks build their tensors at different speeds; the exchange's wait for a
+                                             # peer is bounded (about a second), so they enter the first token together
         with torch.cuda.stream(self.stream):
             self.load_inputs(0)
             self.token(mode)                 # outside capture: allocates the library workspace of this stream
@@ -331,6 +333,11 @@ class Workload:
                 self.token(mode)
             self.graphs[key] = g
         torch.cuda.synchronize()
+
+    def barrier(self):
+        if self.env["dist"] is not None:
+            self.env["dist"].barrier()
+        self.env["torch"].cuda.synchronize()
 
     def retune(self, n_tb, k_chunks):
         """Re-point every config at a context with another thread-block budget and per-projection k_chunk (launch
@@ -346,12 +353,8 @@ class Workload:
         """`steps` graph replays timed with CUDA events on the launching stream; max over ranks."""
         torch, dist, dev = self.env["torch"], self.env["dist"], self.env["dev"]
         g = self.graphs[key]
-
-        def barrier():
-            if dist is not None:
-                dist.barrier()
-            torch.cuda.synchronize()
-
+        barrier = self.barrier
+        barrier()
         with torch.cuda.stream(self.stream):
             for i in range(warm):
                 self.load_inputs(i)

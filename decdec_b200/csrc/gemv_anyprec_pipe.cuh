@@ -75,7 +75,12 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
             uint32_t issued = 0;
             for (uint32_t i = 0; i < nst; ++i) {
                 const uint32_t s = i % S, use = i / S;
-                if (use > 0 && !mbar_wait(bar_empty + 8 * s, (use - 1) & 1u, s_abort, geo.wait_ns)) break;
+                if (use > 0) {
+                    // slots free only after the consumers' wait for the previous kernel: resolve the dependency before
+                    // the first bounded wait (every slot is full by now, so no copy is delayed)
+                    if (use == 1 && s == 0) pdl_wait();
+                    if (!mbar_wait(bar_empty + 8 * s, (use - 1) & 1u, s_abort, geo.wait_ns)) break;
+                }
                 const uint32_t n0 = r0 + i * R;
                 const uint32_t rows = min(R, r1 - n0);
                 const uint32_t full = bar_full + 8 * s;

@@ -221,7 +221,13 @@ __device__ void bcq_pipe_role(const BcqParams& p, const FinParams& f, const Pipe
             tma_prefetch_desc(&maps.b);
             for (uint32_t i = 0; i < n_issue; ++i) {
                 const uint32_t s = i % S, use = i / S;
-                if (use > 0 && !mbar_wait(bar_empty + 8 * s, (use - 1) & 1u, s_abort, geo.wait_ns)) break;
+                if (use > 0) {
+                    // A slot frees only after the consumers have passed their own wait for the previous kernel, which
+                    // may itself be waiting for another GPU: the bounded wait must not run during that time.  Every
+                    // slot is full at this point, so waiting for the dependency here delays no copy.
+                    if (use == 1 && s == 0) pdl_wait();
+                    if (!mbar_wait(bar_empty + 8 * s, (use - 1) & 1u, s_abort, geo.wait_ns)) break;
+                }
                 const uint32_t full = bar_full + 8 * s;
                 mbar_expect_tx(full, tx);
                 const uint32_t n0 = (st0 + i) * kPipeStageN;

@@ -128,6 +128,50 @@ def test_wait_runs_out_and_context_survives(capi):
     capi.call("decdec_tp_destroy", comm)
 
 
+def test_gemv_behind_a_slow_exchange_does_not_give_up(capi):
+    """A GEMV launched behind an exchange becomes resident while the exchange still waits for a peer, and its producer
+    fills every stage slot at once.  Its bounded waits for a free slot must start only after the exchange has ended:
+    here the exchange waits tens of milliseconds for a peer that never pushes (bounded; it reports and returns), the
+    GEMV's own limit is 1 ms, and the GEMV must still finish with the right answer."""
+    from decdec_b200 import ops
+    from tests import problems as P
+    from oracle import forward as ofw
+    os.environ["DECDEC_TP_WAIT_POLLS"] = "60000"
+    try:
+        comm, ptr = _create(capi, 2, 0, 4096)
+    finally:
+        del os.environ["DECDEC_TP_WAIT_POLLS"]
+    _, _, _, nbytes = _layout(capi, 2, 4096)
+    peer = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    capi.call("decdec_tp_connect_ptrs", comm, (C.c_size_t * 2)(ptr, peer.data_ptr()))
+    N, K = 8192, 4096                       # 64 stages per K slice: the producer has to wait for free slots
+    L = P.random_bcq_layer(N, K, 3, 128, seed=5)
+    x = P.make_activation(K, seed=6)
+    qw, al, qb, xd = L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda(), x.cuda()
+    y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+    ops.lutgemm_gemv(xd, torch.zeros_like(y), qw, al, qb, 3, 128)
+    torch.cuda.synchronize()
+    v = torch.randn(4096, device="cuda").half()
+    stream = torch.cuda.current_stream().cuda_stream
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    os.environ["DECDEC_PIPE_WAIT_NS"] = "1000000"
+    try:
+        a.record()
+        capi.call("decdec_tp_allreduce", comm, v.data_ptr(), 4096, DT[v.dtype], stream)
+        b.record()
+        ops.lutgemm_gemv(xd, y, qw, al, qb, 3, 128)
+        torch.cuda.synchronize()
+    finally:
+        del os.environ["DECDEC_PIPE_WAIT_NS"]
+    assert _status(capi, comm)[1] == 1                      # the exchange did give up on its peer ...
+    assert a.elapsed_time(b) > 3.0, "the exchange did not outlast the GEMV's own limit; the test shows nothing"
+    assert ops.stream_status() == 0                         # ... and the GEMV behind it did not
+    want = ofw.layer_output(L["w_hat"], P.to_np(x), None)
+    max_abs, _ = P.errors(y, want)
+    assert max_abs <= 1e-2
+    capi.call("decdec_tp_destroy", comm)
+
+
 def test_argument_checks(capi):
     from decdec_b200.capi import DecdecError
     comm, _ = _create(capi, 2, 0, 1024)

@@ -478,8 +478,9 @@ def run_micro(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     N, K, kind = args.n, args.k, args.micro
+    bits = args.bits
     g = torch.Generator(device=dev).manual_seed(1)
-    wbytes = BITS * N * K / 8
+    wbytes = bits * N * K / 8
     ncopy = max(2, min(32, int(160e6 // wbytes) + 1))
     x = [torch.randn(1, 1, K, device=dev, generator=g).half() for _ in range(8)]
     y = torch.zeros(1, 1, N, dtype=torch.float16, device=dev)
@@ -494,24 +495,24 @@ def run_micro(args):
                                     (torch.rand(N, generator=gc) * 1e-3 + 1e-4).half(),
                                     torch.sort(torch.randn(K, generator=gc).abs() * 3, descending=True).values.half())
     if "lutgemm" in kind:
-        w = [(ri(K // 32, BITS, N), (torch.rand(K // GROUP, BITS, N, device=dev, generator=g) * 0.01).half(),
+        w = [(ri(K // 32, bits, N), (torch.rand(K // GROUP, bits, N, device=dev, generator=g) * 0.01).half(),
               ((torch.rand(K // GROUP, N, device=dev, generator=g) - 0.5) * 0.01).half()) for _ in range(ncopy)]
         hbm = gemv_bytes(N, K)
         if kind == "lutgemm":
-            call = lambda i: ext.lutgemm_gemv(x[i % 8], y, *w[i % ncopy], BITS, GROUP)
+            call = lambda i: ext.lutgemm_gemv(x[i % 8], y, *w[i % ncopy], bits, GROUP)
         else:
-            call = lambda i: ext.dec_lutgemm(cfg, x[i % 8], y, *w[i % ncopy], BITS, GROUP)
+            call = lambda i: ext.dec_lutgemm(cfg, x[i % 8], y, *w[i % ncopy], bits, GROUP)
     elif "anyprec" in kind:
-        w = [(ri(BITS, N, K // 32), (torch.randn(N, 2 ** BITS, device=dev, generator=g) * 0.02).half()) for _ in range(ncopy)]
-        hbm = BITS * N * K / 8 + N * 2 ** BITS * 2 + 2 * K + 4 * N
+        w = [(ri(bits, N, K // 32), (torch.randn(N, 2 ** bits, device=dev, generator=g) * 0.02).half()) for _ in range(ncopy)]
+        hbm = bits * N * K / 8 + N * 2 ** bits * 2 + 2 * K + 4 * N
         if kind == "anyprec":
-            call = lambda i: ext.anyprec_gemv(x[i % 8], y, *w[i % ncopy], BITS)
+            call = lambda i: ext.anyprec_gemv(x[i % 8], y, *w[i % ncopy], bits)
         else:
-            call = lambda i: ext.dec_anyprec(cfg, x[i % 8], y, *w[i % ncopy], BITS)
+            call = lambda i: ext.dec_anyprec(cfg, x[i % 8], y, *w[i % ncopy], bits)
     elif kind == "sqllm":
-        w = [(ri(K * BITS // 32, N), (torch.randn(N, 2 ** BITS, device=dev, generator=g) * 0.02).half()) for _ in range(ncopy)]
-        hbm = BITS * N * K / 8 + N * 2 ** BITS * 2 + 2 * K + 4 * N
-        call = lambda i: ext.sqllm_gemv(x[i % 8], y, *w[i % ncopy], BITS)
+        w = [(ri(K * bits // 32, N), (torch.randn(N, 2 ** bits, device=dev, generator=g) * 0.02).half()) for _ in range(ncopy)]
+        hbm = bits * N * K / 8 + N * 2 ** bits * 2 + 2 * K + 4 * N
+        call = lambda i: ext.sqllm_gemv(x[i % 8], y, *w[i % ncopy], bits)
     elif kind == "dec":
         hbm = 0
         call = lambda i: ext.dec(cfg, x[i % 8], y)
@@ -568,6 +569,7 @@ def main():
                     help="multi-GPU: exchange of the row-parallel outputs (push = one-shot kernel over NVLink peer memory)")
     ap.add_argument("--no-config4", action="store_true", help="skip the Llama-3-70B-shaped measurement")
     ap.add_argument("--config4-layers", type=int, default=0, help="layers of the Llama-3-70B-shaped model (0 = all 80)")
+    ap.add_argument("--bits", type=int, default=BITS, help="bit width of the --micro entry point")
     ap.add_argument("--micro", default="", help="single entry point: lutgemm | dec_lutgemm | anyprec | dec_anyprec | sqllm | dec")
     ap.add_argument("--n", type=int, default=28672)
     ap.add_argument("--k", type=int, default=4096)

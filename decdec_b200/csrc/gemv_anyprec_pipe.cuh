@@ -1,16 +1,20 @@
-// Any-precision 3-bit GEMV role, bulk-copy pipelined variant.
+// Any-precision GEMV role for 3 to 8 bits, bulk-copy pipelined variant.
 //
-// Arithmetic of gemv_anyprec.cuh:ap3_role (register-resident byte tables, byte-permute lookups,
-// activations staged in pair order), fed differently: in the tensor [plane][row][K/32] consecutive
-// rows of one plane are contiguous, so a stage of R rows is three contiguous runs (one per plane) plus
-// the R LUT rows.  A producer thread moves them with four 1-D bulk asynchronous copies
-// (cp.async.bulk, 6-8 KB each, completion counted on an mbarrier) several stages ahead of sixteen
-// consumer warps; a warp's work item is (row of the stage, 4096-channel segment of that row).
+// In the tensor [plane][row][K/32] consecutive rows of one plane are contiguous, so a stage of R rows is one
+// contiguous run per plane plus the R LUT rows.  A producer thread moves them with 1-D bulk asynchronous
+// copies (cp.async.bulk, completion counted on an mbarrier) several stages ahead of the consumer warps;
+// a warp's work item is (row of the stage, 4096-channel segment of that row).
+// Two decoders.  The 3-bit byte-permute decoder has the arithmetic of gemv_anyprec.cuh:ap3_role (register-
+// resident byte tables, activations staged in pair order).  The lookup decoder serves every width: the plane
+// words of 32 channels are regrouped into 4-bit fields with a handful of logic operations, each code indexes
+// the row's LUT where the bulk copy landed it in shared memory (a row of up to 64 entries spans at most 32 banks
+// and equal entries broadcast, so a warp's lookup is one wavefront), and the product goes into one of four fp32
+// sums with a mixed-precision multiply-add (16-bit factors, fp32 accumulator): no 16-bit partial sums.
 // A CTA owns its rows completely (all of K), so the row sums meet in a small shared-memory buffer and the
 // CTA folds them into y itself: GEMV-only launches use no global accumulator, ticket or fence.  Fused
 // launches store the sums into the workspace accumulator and arrive on the tile's ticket, where they meet
 // the compensation CTAs.
-// Requirements: bits == 3, K % 128 == 0, K <= 32768.  Every mbarrier wait is bounded.
+// Requirements: K % 128 == 0, K <= 32768.  Every mbarrier wait is bounded.
 #pragma once
 #include "gemv_anyprec.cuh"
 #include "gemv_bcq_pipe.cuh"
@@ -24,6 +28,7 @@ struct ApPipeGeom {
     uint32_t segs;             // ceil(K / 4096): warps per row
     uint32_t stages;           // pipeline depth
     uint32_t stage_bytes;
+    uint32_t lookup;           // 1: lookup decoder, 0: byte-permute decoder (3 bits only)
     uint32_t x_bytes;          // staged activations (rounded to 128)
     uint32_t rows_per_cta;     // multiple of R
     uint32_t part_bytes;       // row sums of the CTA (fp32, rounded to 128 bytes)
@@ -34,8 +39,68 @@ struct ApPipeGeom {
 
 constexpr int kApPipeHdr = 256;   // [abort, flag][full barriers 8][empty barriers 8]
 
+// 4-bit fields from up to four plane words: field t (bits 4t..4t+3) of result ph holds, most significant plane
+// first, the bits that planes P[0..B-1] carry at position 4t + ph.
+template <int B>
+__device__ __forceinline__ void ap_fields(const uint32_t* P, uint32_t (&V)[4]) {
+    uint32_t R[B];
+#pragma unroll
+    for (int i = 0; i < B; ++i) R[i] = i ? __funnelshift_r(P[i], P[i], i) : P[0];
+#pragma unroll
+    for (int ph = 0; ph < 4; ++ph) {
+        uint32_t m = 0u;
+#pragma unroll
+        for (int i = 0; i < B; ++i) m |= R[i] & (0x11111111u << ((ph - i) & 3));
+        const int rot = (B - 1 - ph) & 31;
+        V[ph] = rot ? __funnelshift_l(m, m, rot) : m;
+    }
+}
+
+// d += a * b with 16-bit factors (raw bits of the element type) and an fp32 accumulator
 template <int DT>
-__device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPipeGeom& geo, uint32_t cta, unsigned char* sm) {
+__device__ __forceinline__ void ap_mixed_fma(float& d, uint16_t a, uint16_t b) {
+    if constexpr (DT == FP16) asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(d) : "h"(a), "h"(b));
+    else asm("fma.rn.f32.bf16 %0, %1, %2, %0;" : "+f"(d) : "h"(a), "h"(b));
+}
+
+// One plane-word position (32 channels) of one row through the lookup decoder.  `lutrow` is the row's LUT where the
+// bulk copy landed it; X[j] holds the activations of channels 8 * E * j + (0..7) of the word's group.
+template <int DT, int BITS>
+__device__ __forceinline__ void ap_lookup_word(const uint32_t* q, const unsigned char* lutrow, const uint4 (&X)[4], float (&acc)[4]) {
+    constexpr int BH = BITS < 4 ? BITS : 4, BL = BITS - BH;
+    uint32_t Vh[4], Vl[4] = {0u, 0u, 0u, 0u};
+    ap_fields<BH>(q, Vh);
+    if constexpr (BL > 0) ap_fields<BL>(q + 4, Vl);
+#pragma unroll
+    for (int ph = 0; ph < 4; ++ph) {
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+            const int pos = 31 - (4 * t + ph);          // channel = 8 * E * (pos / 8) + pos % 8 inside the word's group
+            const int jj = pos >> 3, r = pos & 7;
+            uint32_t off;                                // byte offset of the code's entry: 2 * code
+            if constexpr (BL == 0) {
+                off = t ? ((Vh[ph] >> (4 * t - 1)) & 0x1eu) : ((Vh[ph] << 1) & 0x1eu);
+            } else {
+                constexpr uint32_t mh = 0xfu << (BL + 1), ml = ((1u << BL) - 1u) << 1;
+                const int sh = 4 * t - BL - 1;
+                off = (sh >= 0) ? ((Vh[ph] >> (sh & 31)) & mh) : ((Vh[ph] << ((-sh) & 31)) & mh);
+                off |= t ? ((Vl[ph] >> (4 * t - 1)) & ml) : ((Vl[ph] << 1) & ml);
+            }
+            const uint16_t w = *reinterpret_cast<const uint16_t*>(lutrow + off);
+            const uint32_t xw = (&X[jj].x)[r >> 1];
+            const uint16_t xv = (r & 1) ? (uint16_t)(xw >> 16) : (uint16_t)(xw & 0xffffu);
+            ap_mixed_fma<DT>(acc[t & 3], w, xv);
+        }
+    }
+}
+
+// BITS planes; LOOKUP selects the decoder (the byte-permute decoder exists for 3 bits only)
+template <int DT, int BITS, bool LOOKUP>
+__device__ void ap_pipe_role(const ApParams& p, const FinParams& f, const ApPipeGeom& geo, uint32_t cta, unsigned char* sm) {
+    static_assert(LOOKUP || BITS == 3, "the byte-permute decoder is 3-bit");
+    constexpr uint32_t kLutRow = 2u << BITS;             // bytes of one row's LUT
+    constexpr int NW = 16;                               // consumer warps; warp NW is the producer
+    constexpr int NT = (NW + 1) * 32;
     using T = typename Tr<DT>::T;
     static_assert(DT != FP32, "any-precision kernels take fp16/bf16 only");
     volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(sm);
@@ -53,21 +118,21 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
     const uint32_t r0 = cta * geo.rows_per_cta;
     const uint32_t r1 = min(p.N, r0 + geo.rows_per_cta);
     const uint32_t nst = (r1 - r0 + R - 1) / R;
-    const uint32_t lut_off = 3 * R * rowbytes;          // LUT rows sit after the three plane runs
+    const uint32_t lut_off = BITS * R * rowbytes;       // LUT rows sit after the plane runs
 
     pdl_trigger();
     if (tid == 0) {
         *s_abort = 0u;
         for (uint32_t s = 0; s < S; ++s) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 16);
+            mbar_init(bar_empty + 8 * s, NW);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (uint32_t i = tid; i < geo.rows_per_cta; i += kApPipeThreads) part[i] = 0.0f;
+    for (uint32_t i = tid; i < geo.rows_per_cta; i += NT) part[i] = 0.0f;
     __syncthreads();
 
-    if (warp == 16) {
+    if (warp == NW) {
         // ------------------------------ producer (one elected lane) -----------------------------
         if (lane == 0) {
             const size_t plane_stride = (size_t)p.N * nwords;
@@ -84,12 +149,12 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
                 const uint32_t n0 = r0 + i * R;
                 const uint32_t rows = min(R, r1 - n0);
                 const uint32_t full = bar_full + 8 * s;
-                mbar_expect_tx(full, rows * (3 * rowbytes + 16));
+                mbar_expect_tx(full, rows * (BITS * rowbytes + kLutRow));
                 const uint32_t dst = smem_u32(stage0 + (size_t)s * geo.stage_bytes);
 #pragma unroll
-                for (int pl = 0; pl < 3; ++pl)
+                for (int pl = 0; pl < BITS; ++pl)
                     bulk_g2s(dst + pl * R * rowbytes, p.qweight + pl * plane_stride + (size_t)n0 * nwords, rows * rowbytes, full);
-                bulk_g2s(dst + lut_off, lutb + (size_t)n0 * 16, rows * 16, full);
+                bulk_g2s(dst + lut_off, lutb + (size_t)n0 * kLutRow, rows * kLutRow, full);
                 issued = i + 1;
             }
             if (*s_abort) {
@@ -100,8 +165,61 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
                 }
             }
         }
+    } else if constexpr (LOOKUP) {
+        // ------------------------------ consumers, lookup decoder -------------------------------
+        pdl_wait();     // weights are already streaming (producer warp); activations come from earlier kernels
+        const T* x = reinterpret_cast<const T*>(p.x);
+        for (uint32_t k = tid; k < p.K; k += 512) sx[k] = x[k];
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+
+        const uint32_t tailE = nwords & 31u, nfull = nwords >> 5;
+        const uint32_t row_in_stage = warp / geo.segs, seg = warp % geo.segs;
+        const bool has_item = row_in_stage < R;
+        const uint32_t wi0 = seg * 128 + lane;            // the lane's words: wi0 + 32 * u, u = 0..3
+        const bool lane_active = has_item && wi0 < nwords;
+
+        for (uint32_t i = 0; i < nst; ++i) {
+            const uint32_t s = i % S;
+            if (!mbar_wait(bar_full + 8 * s, (i / S) & 1u, s_abort, geo.wait_ns)) break;
+            const unsigned char* st = stage0 + (size_t)s * geo.stage_bytes;
+            const uint32_t n = r0 + i * R + row_in_stage;
+            float facc = 0.0f;
+            if (lane_active && n < r1) {
+                const unsigned char* lutrow = st + lut_off + row_in_stage * kLutRow;
+                const uint32_t* rowp = reinterpret_cast<const uint32_t*>(st + (size_t)row_in_stage * rowbytes) + wi0;
+                uint32_t q[4][BITS];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const bool ok = wi0 + 32 * u < nwords;
+#pragma unroll
+                    for (int pl = 0; pl < BITS; ++pl) q[u][pl] = ok ? rowp[32 * u + pl * R * nwords] : 0u;
+                }
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t wi = wi0 + 32 * u;
+                    if (wi >= nwords) break;
+                    const uint32_t blk = wi >> 5, t = wi & 31u;
+                    const uint32_t E = (blk == nfull) ? tailE : 32u;
+                    const T* xb = sx + blk * 1024u + 8u * t;
+                    uint4 X[4];
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) X[jj] = *reinterpret_cast<const uint4*>(xb + 8u * E * jj);
+                    ap_lookup_word<DT, BITS>(q[u], lutrow, X, acc);
+                }
+                facc = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);      // the stage (plane words and LUT row) is no longer read
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) facc += __shfl_xor_sync(0xffffffffu, facc, d);
+            if (lane == 0 && has_item && n < r1) {
+                if (geo.segs == 1) part[n - r0] = facc;           // one warp per row: nobody else writes it
+                else atomicAdd(&part[n - r0], facc);              // the K segments of a row meet here
+            }
+        }
     } else {
-        // ------------------------------ consumers ----------------------------------------------
+        // ------------------------------ consumers, byte-permute decoder -------------------------
         pdl_wait();     // weights are already streaming (producer warp); activations come from earlier kernels
         const T* x = reinterpret_cast<const T*>(p.x);
         for (uint32_t k = tid; k < p.K; k += 512) sx[(k & ~7u) | ap_perm(k & 7u)] = x[k];
@@ -185,7 +303,7 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
             }
         }
     }
-    if (warp == 16) pdl_wait();     // the producer warp touches the accumulator and y only from here on
+    if (warp == NW) pdl_wait();     // the producer warp touches the accumulator and y only from here on
     // fold the CTA's rows: four consecutive outputs per thread; y is read before the barrier so that the
     // load overlaps the last warps' work
     T* y = reinterpret_cast<T*>(f.y);
@@ -205,7 +323,7 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
     if (geo.direct) {
         if (!*s_abort) {            // an unfinished launch leaves y alone
             if (yvec) {
-                for (uint32_t i = 4u * tid; i < nrows; i += 4u * kApPipeThreads) {
+                for (uint32_t i = 4u * tid; i < nrows; i += 4u * NT) {
                     const float4 v = *reinterpret_cast<const float4*>(part + i);
                     float o[4];
                     if (pre && i == 4u * (uint32_t)tid) { o[0] = y0[0]; o[1] = y0[1]; o[2] = y0[2]; o[3] = y0[3]; }
@@ -223,7 +341,7 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
                     *reinterpret_cast<uint2*>(y + r0 + i) = raw;
                 }
             } else {
-                for (uint32_t i = tid; i < nrows; i += kApPipeThreads)
+                for (uint32_t i = tid; i < nrows; i += NT)
                     y[r0 + i] = Tr<DT>::from_f(Tr<DT>::to_f(y[r0 + i]) + part[i]);
             }
         }
@@ -231,8 +349,8 @@ __device__ void ap3_pipe_role(const ApParams& p, const FinParams& f, const ApPip
     }
     // fused launch: the sums go to the accumulator (this CTA is their only GEMV writer) and the CTA arrives on its
     // tile even after a failed wait, so that the workspace stays consistent
-    for (uint32_t i = tid; i < nrows; i += kApPipeThreads) __stcg(f.acc + r0 + i, part[i]);
-    arrive_and_finalize<DT>(f, cta, cta + 1, s_flag, kApPipeThreads);
+    for (uint32_t i = tid; i < nrows; i += NT) __stcg(f.acc + r0 + i, part[i]);
+    arrive_and_finalize<DT>(f, cta, cta + 1, s_flag, NT);
 }
 
 }  // namespace dd

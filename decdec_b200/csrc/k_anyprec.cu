@@ -42,39 +42,52 @@ cudaError_t launch_anyprec(int dt, const ApParams& g, const DecParams& d, const 
     return fast3 ? go<BF16, true>(g, d, f, s) : go<BF16, false>(g, d, f, s);
 }
 
-template <int DT>
+template <int DT, int BITS, bool LOOKUP>
 __global__ void __launch_bounds__(kApPipeThreads, 1)
 k_anyprec_pipe(const __grid_constant__ ApParams g, const __grid_constant__ DecParams d, const __grid_constant__ FinParams f,
                const __grid_constant__ ApPipeGeom geo) {
     extern __shared__ __align__(128) unsigned char sm[];
     if (blockIdx.x < d.n_cta) dec_role<DT>(d, f, blockIdx.x, sm);
-    else ap3_pipe_role<DT>(g, f, geo, blockIdx.x - d.n_cta, sm);
+    else ap_pipe_role<DT, BITS, LOOKUP>(g, f, geo, blockIdx.x - d.n_cta, sm);
 }
 
-// Stage geometry of the pipelined 3-bit kernel; false if the shape is not eligible.
+// Which decoder a 3-bit launch takes: the register-table one unless DECDEC_AP3_DECODER=lookup.
+static bool ap_lookup_decoder(uint32_t bits) {
+    if (bits != 3) return true;
+    const char* v = getenv("DECDEC_AP3_DECODER");
+    return v && *v == 'l';
+}
+
+// Stage geometry of the pipelined kernel (3 to 8 bits); false if the shape is not eligible.
 bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* geo, uint32_t sm_budget) {
-    if (bits != 3 || K % 128u || K > 32768u || N == 0) return false;
+    if (bits < 3 || bits > 8 || K % 128u || K > 32768u || N == 0) return false;
+    const bool lookup = ap_lookup_decoder(bits);
     const uint32_t rowbytes = K / 8;
+    const uint32_t per_row = bits * rowbytes + (2u << bits);      // plane words and the LUT row
     geo->segs = (K + 4095) / 4096;
     uint32_t R = 16 / geo->segs;
     if (R == 0) return false;
     while (R & (R - 1)) R &= R - 1;                      // largest power of two <= 16 / segs
-    geo->rows_per_stage = R;
+    geo->lookup = lookup ? 1u : 0u;
     geo->x_bytes = (K * 2 + 127u) & ~127u;
-    geo->stage_bytes = (R * (3 * rowbytes + 16) + 127u) & ~127u;
     if (sm_budget == 0) sm_budget = 1;
     uint32_t rows = (N + sm_budget - 1) / sm_budget;
     rows = ((rows + 31) / 32) * 32;
     geo->rows_per_cta = rows;
     geo->part_bytes = (rows * 4u + 127u) & ~127u;
-    if (kApPipeHdr + geo->x_bytes + geo->part_bytes + 2u * geo->stage_bytes > 227u * 1024u) return false;
-    const uint32_t budget = 227 * 1024 - kApPipeHdr - geo->x_bytes - geo->part_bytes;
+    const uint32_t fixed = kApPipeHdr + geo->x_bytes + geo->part_bytes;
+    if (fixed >= 227u * 1024u) return false;
+    const uint32_t budget = 227 * 1024 - fixed;
+    // wide rows: fewer rows per stage until two stages fit (some consumer warps then have no work item)
+    while (R > 1 && 2u * ((R * per_row + 127u) & ~127u) > budget) R >>= 1;
+    geo->rows_per_stage = R;
+    geo->stage_bytes = (R * per_row + 127u) & ~127u;
     uint32_t smax = budget / geo->stage_bytes;
     if (smax > 8) smax = 8;
     if (smax < 2) return false;
     const uint32_t nst = rows / R;
     geo->stages = nst < smax ? nst : smax;
-    geo->smem_bytes = kApPipeHdr + geo->x_bytes + geo->part_bytes + geo->stages * geo->stage_bytes;
+    geo->smem_bytes = fixed + geo->stages * geo->stage_bytes;
     geo->direct = 0;        // set by the caller
     {
         const char* w = getenv("DECDEC_PIPE_WAIT_NS");
@@ -84,17 +97,15 @@ bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* ge
     return true;
 }
 
-cudaError_t launch_anyprec_pipe(int dt, const ApParams& g, const DecParams& d, const FinParams& f, const ApPipeGeom& geo, cudaStream_t s) {
-    static bool configured[64][2] = {};
+template <int DT, int BITS, bool LOOKUP>
+static cudaError_t go_pipe(const ApParams& g, const DecParams& d, const FinParams& f, const ApPipeGeom& geo, cudaStream_t s) {
+    static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    const int di = dt == FP16 ? 0 : 1;
-    if (dev < 64 && !configured[dev][di]) {
-        cudaError_t e = dt == FP16
-            ? cudaFuncSetAttribute(k_anyprec_pipe<FP16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)
-            : cudaFuncSetAttribute(k_anyprec_pipe<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_anyprec_pipe<DT, BITS, LOOKUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
-        configured[dev][di] = true;
+        configured[dev] = true;
     }
     // programmatic dependent launch: thread blocks may become resident (and prefetch weights) while the
     // previous kernel of the stream drains; the kernel waits for it before touching activations or outputs
@@ -109,8 +120,24 @@ cudaError_t launch_anyprec_pipe(int dt, const ApParams& g, const DecParams& d, c
     attr[0].val.programmaticStreamSerializationAllowed = (e && *e == '0') ? 0 : 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (dt == FP16) return cudaLaunchKernelEx(&cfg, k_anyprec_pipe<FP16>, g, d, f, geo);
-    return cudaLaunchKernelEx(&cfg, k_anyprec_pipe<BF16>, g, d, f, geo);
+    return cudaLaunchKernelEx(&cfg, k_anyprec_pipe<DT, BITS, LOOKUP>, g, d, f, geo);
+}
+
+template <int DT>
+static cudaError_t pipe_by_bits(const ApParams& g, const DecParams& d, const FinParams& f, const ApPipeGeom& geo, cudaStream_t s) {
+    switch (g.bits) {
+        case 3: return geo.lookup ? go_pipe<DT, 3, true>(g, d, f, geo, s) : go_pipe<DT, 3, false>(g, d, f, geo, s);
+        case 4: return go_pipe<DT, 4, true>(g, d, f, geo, s);
+        case 5: return go_pipe<DT, 5, true>(g, d, f, geo, s);
+        case 6: return go_pipe<DT, 6, true>(g, d, f, geo, s);
+        case 7: return go_pipe<DT, 7, true>(g, d, f, geo, s);
+        case 8: return go_pipe<DT, 8, true>(g, d, f, geo, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_anyprec_pipe(int dt, const ApParams& g, const DecParams& d, const FinParams& f, const ApPipeGeom& geo, cudaStream_t s) {
+    return dt == FP16 ? pipe_by_bits<FP16>(g, d, f, geo, s) : pipe_by_bits<BF16>(g, d, f, geo, s);
 }
 
 cudaError_t launch_ap_dequant(int dt, const uint32_t* qweight, const void* lut, void* out, uint32_t N, uint32_t K,

@@ -449,8 +449,15 @@ def test_dec_sqllm(ops, bits):
     (200, 1024 + 128, 3),   # ragged N, small tail
     (128, 96, 3),           # K below one block and not a multiple of 128 -> generic path
     (128, 2048, 4),
-    (64, 1056, 5),
+    (64, 1056, 5),          # K not a multiple of 128 -> generic path
     (64, 1024, 8),
+    (4096, 4096, 4),        # pipelined lookup decoder at every width
+    (1000, 14336, 4),       # ragged N, four K segments per row
+    (512, 4096 + 640, 5),   # tail block
+    (512, 4096, 6),
+    (256, 2048, 7),
+    (512, 14336, 8),        # widest rows: fewer rows per stage
+    (64, 28672, 8),
 ])
 def test_anyprec_gemv(ops, dtype, N, K, bits):
     L = P.lut_layer(N, K, bits, seed=N + K + bits, dtype=dtype, real=(bits == 3 and N <= 1024))

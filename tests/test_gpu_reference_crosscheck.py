@@ -433,6 +433,12 @@ def test_reference_kernel_timings(ref, ops):
         row["lutgemm_gemv new"] = _time_us(lambda i: ext.lutgemm_gemv(x, y, *wb[i % ncopy], 3, 128), ncopy)
         row["anyprec_gemv ref"] = _time_us(lambda i: ref.anyprec_gemv(x, y, *wa[i % ncopy], 3), ncopy)
         row["anyprec_gemv new"] = _time_us(lambda i: ext.anyprec_gemv(x, y, *wa[i % ncopy], 3), ncopy)
+        if N * K <= 6144 * 4096 or K == 4096:
+            n4 = max(2, min(ncopy, 4))
+            w4 = [(ri(4, N, K // 32), (torch.randn(N, 16, device=dev, generator=g) * 0.02).half()) for _ in range(n4)]
+            row["anyprec_gemv 4-bit ref"] = _time_us(lambda i: ref.anyprec_gemv(x, y, *w4[i % n4], 4), n4)
+            row["anyprec_gemv 4-bit new"] = _time_us(lambda i: ext.anyprec_gemv(x, y, *w4[i % n4], 4), n4)
+            del w4
         row["dec kc8 ref"] = _time_us(lambda i: ref.dec(cfg_r, x, y), 1)
         row["dec kc8 new"] = _time_us(lambda i: ext.dec(cfg_n, x, y), 1)
         row["dec_lutgemm kc8 ref"] = _time_us(lambda i: ref.dec_lutgemm(cfg_r, x, y, *wb[i % ncopy], 3, 128), ncopy)

@@ -355,11 +355,11 @@ int run_anyprec(Config* c, const void* x, void* y, const int32_t* qw, uint32_t p
     uint32_t tile_units = cdiv(units, target);
     tile_units = env_u32("DECDEC_AP_TILE_UNITS", tile_units);
     ApPipeGeom pgeo;
-    const bool pipe = env_u32("DECDEC_AP_PIPE", 1) && anyprec_pipe_geometry(N, K, g.bits, &pgeo, gemv_sm_budget(c, true));
-    if (pipe) tile_units = pgeo.rows_per_cta / 32;
+    const bool pipe = env_u32("DECDEC_AP_PIPE", 1) && anyprec_pipe_geometry(N, K, g.bits, &pgeo, gemv_sm_budget(c, true), c == nullptr);
+    if (pipe) tile_units = cdiv(pgeo.rows_per_cta, 32);
     FinParams f;
     if (int r = setup_fin(&f, ws, y, N, tile_units, 1)) return r;
-    g.n_cta = f.n_tiles;
+    g.n_cta = (pipe && c == nullptr) ? cdiv(N, pgeo.rows_per_cta) : f.n_tiles;   // no finalizer tiles in a GEMV-only launch
     DecParams d;
     memset(&d, 0, sizeof(d));
     if (c) {

@@ -16,7 +16,7 @@ bool bcq_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t group, in
                        uint32_t sm_budget);   // SMs the GEMV thread blocks may fill in one wave
 cudaError_t launch_bcq_pipe(int dt, const BcqParams& g, const DecParams& d, const FinParams& f, const PipeGeom& geo, cudaStream_t s);
 cudaError_t launch_anyprec(int dt, const ApParams& g, const DecParams& d, const FinParams& f, cudaStream_t s);
-bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* geo, uint32_t sm_budget = 148);
+bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* geo, uint32_t sm_budget = 148, bool gemv_only = false);
 cudaError_t launch_anyprec_pipe(int dt, const ApParams& g, const DecParams& d, const FinParams& f, const ApPipeGeom& geo, cudaStream_t s);
 cudaError_t launch_sqllm(int dt, const SqParams& g, const DecParams& d, const FinParams& f, cudaStream_t s);
 cudaError_t launch_ap_dequant(int dt, const uint32_t* qweight, const void* lut, void* out, uint32_t N, uint32_t K,

@@ -58,8 +58,11 @@ static bool ap_lookup_decoder(uint32_t bits) {
     return v && *v == 'l';
 }
 
-// Stage geometry of the pipelined kernel (3 to 8 bits); false if the shape is not eligible.
-bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* geo, uint32_t sm_budget) {
+// Stage geometry of the pipelined kernel (3 to 8 bits); false if the shape is not eligible.  A CTA's rows are a whole
+// number of 32-output finalizer tiles when a compensation role may share the launch; a GEMV-only launch (no config)
+// has no finalizer and cuts the rows in multiples of 16, which fills the SMs more evenly (6144 rows: 128 CTAs of 48
+// instead of 96 of 64).
+bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* geo, uint32_t sm_budget, bool gemv_only) {
     if (bits < 3 || bits > 8 || K % 128u || K > 32768u || N == 0) return false;
     const bool lookup = ap_lookup_decoder(bits);
     const uint32_t rowbytes = K / 8;
@@ -72,7 +75,8 @@ bool anyprec_pipe_geometry(uint32_t N, uint32_t K, uint32_t bits, ApPipeGeom* ge
     geo->x_bytes = (K * 2 + 127u) & ~127u;
     if (sm_budget == 0) sm_budget = 1;
     uint32_t rows = (N + sm_budget - 1) / sm_budget;
-    rows = ((rows + 31) / 32) * 32;
+    const uint32_t gran = gemv_only ? 16u : 32u;
+    rows = ((rows + gran - 1) / gran) * gran;
     geo->rows_per_cta = rows;
     geo->part_bytes = (rows * 4u + 127u) & ~127u;
     const uint32_t fixed = kApPipeHdr + geo->x_bytes + geo->part_bytes;

@@ -355,7 +355,16 @@ int run_anyprec(Config* c, const void* x, void* y, const int32_t* qw, uint32_t p
     uint32_t tile_units = cdiv(units, target);
     tile_units = env_u32("DECDEC_AP_TILE_UNITS", tile_units);
     ApPipeGeom pgeo;
-    const bool pipe = env_u32("DECDEC_AP_PIPE", 1) && anyprec_pipe_geometry(N, K, g.bits, &pgeo, gemv_sm_budget(c, true), c == nullptr);
+    uint32_t budget = gemv_sm_budget(c, true);
+    if (c) {
+        // many compensation thread blocks (the launch is bound by the host link): the GEMV runs in the SMs they leave
+        // free and takes over the rest as they retire, which it does more evenly in thread blocks a third the size
+        DecParams dg;
+        memset(&dg, 0, sizeof(dg));
+        dec_geometry(c, true, 1u << 20, &dg);
+        if (dg.n_cta > device_sms() / 4 + 3) budget *= env_u32("DECDEC_AP_FUSED_SPLIT", 3);
+    }
+    const bool pipe = env_u32("DECDEC_AP_PIPE", 1) && anyprec_pipe_geometry(N, K, g.bits, &pgeo, budget, c == nullptr);
     if (pipe) tile_units = cdiv(pgeo.rows_per_cta, 32);
     FinParams f;
     if (int r = setup_fin(&f, ws, y, N, tile_units, 1)) return r;

@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <vector>
 #include <mutex>
 #include <utility>
 
@@ -60,6 +61,8 @@ struct Workspace {
 std::mutex g_mu;
 std::map<std::pair<int, cudaStream_t>, Workspace> g_ws;
 std::map<int, Workspace> g_ws_first;                       // first workspace of a device: capture fallback
+std::map<int, std::vector<Workspace>> g_ws_spare;          // set aside for streams first seen while capturing
+constexpr int kSpareWorkspaces = 4;
 std::map<int, std::pair<cudaStream_t, std::pair<cudaEvent_t, cudaEvent_t>>> g_side;   // dummy_* side stream
 
 // A launch that gave up on a wait left its code in the workspace's error word: every later call on that stream
@@ -72,24 +75,8 @@ int check_ws(const Workspace& w) {
     return 0;
 }
 
-int get_workspace(cudaStream_t stream, Workspace* out) {
-    int dev = 0;
-    DD_CUDA(cudaGetDevice(&dev));
-    std::lock_guard<std::mutex> lk(g_mu);
-    auto it = g_ws.find({dev, stream});
-    if (it != g_ws.end()) { *out = it->second; return check_ws(*out); }
-    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-    DD_CUDA(cudaStreamIsCapturing(stream, &cs));
-    if (cs != cudaStreamCaptureStatusNone) {
-        // no allocation while capturing: reuse the device's first workspace (captured work of one
-        // graph is ordered, so sharing is safe as long as that graph is not replayed concurrently
-        // with eager calls on the stream that owns the workspace)
-        auto f = g_ws_first.find(dev);
-        if (f == g_ws_first.end())
-            return fail(DECDEC_E_INVALID, "first call on a device must happen outside stream capture (workspace allocation)");
-        *out = f->second;
-        return check_ws(*out);
-    }
+// Allocates and clears one workspace (never called while a stream of the device is capturing).
+static int alloc_workspace(Workspace* out) {
     Workspace w;
     if (cudaMalloc(&w.acc, 2 * kAccCap * sizeof(float)) != cudaSuccess) return fail(DECDEC_E_NOMEM, "cudaMalloc(accumulator) failed");
     if (cudaMalloc(&w.tickets, (kTicketCap + 4) * sizeof(unsigned)) != cudaSuccess) { cudaFree(w.acc); return fail(DECDEC_E_NOMEM, "cudaMalloc(tickets) failed"); }
@@ -110,9 +97,48 @@ int get_workspace(cudaStream_t stream, Workspace* out) {
         w.err = reinterpret_cast<unsigned*>(d);
         w.err_host = reinterpret_cast<volatile unsigned*>(h);
     }
+    *out = w;
+    return 0;
+}
+
+int get_workspace(cudaStream_t stream, Workspace* out) {
+    int dev = 0;
+    DD_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_ws.find({dev, stream});
+    if (it != g_ws.end()) { *out = it->second; return check_ws(*out); }
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    DD_CUDA(cudaStreamIsCapturing(stream, &cs));
+    if (cs != cudaStreamCaptureStatusNone) {
+        // no allocation while capturing.  A stream first seen during capture (frameworks capture on streams of their
+        // own) gets one of the spare workspaces set aside at the device's first call, so that graphs captured on
+        // different streams do not share accumulators; when the spares are used up it shares the device's first
+        // workspace (then that graph must not run concurrently with work on the owning stream).
+        auto sp = g_ws_spare.find(dev);
+        if (sp != g_ws_spare.end() && !sp->second.empty()) {
+            *out = sp->second.back();
+            sp->second.pop_back();
+            g_ws[{dev, stream}] = *out;
+            return check_ws(*out);
+        }
+        auto f = g_ws_first.find(dev);
+        if (f == g_ws_first.end())
+            return fail(DECDEC_E_INVALID, "first call on a device must happen outside stream capture (workspace allocation)");
+        *out = f->second;
+        return check_ws(*out);
+    }
+    Workspace w;
+    if (int r = alloc_workspace(&w)) return r;
+    if (!g_ws_first.count(dev)) {
+        g_ws_first[dev] = w;
+        for (int i = 0; i < kSpareWorkspaces; ++i) {
+            Workspace sw;
+            if (alloc_workspace(&sw)) break;            // fewer spares: later captures share the first workspace
+            g_ws_spare[dev].push_back(sw);
+        }
+    }
     DD_CUDA(cudaDeviceSynchronize());
     g_ws[{dev, stream}] = w;
-    if (!g_ws_first.count(dev)) g_ws_first[dev] = w;
     *out = w;
     return 0;
 }

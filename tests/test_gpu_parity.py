@@ -635,6 +635,42 @@ def test_residual_on_device_and_graph_capture(ops):
         _assert_close(y, ofw.layer_output(L["w_hat"], P.to_np(x), None, delta), "fp16", "graph replay")
 
 
+def test_graphs_captured_on_fresh_streams_have_their_own_workspace(ops):
+    """A stream that the library first sees during capture cannot allocate; it is given one of the workspaces set aside
+    at the device's first call.  Two graphs captured on two such streams, with layers of the same width (so that they
+    would meet on the same accumulator words if they shared a workspace), are replayed side by side on two streams many
+    times and must both keep giving the eager result bit for bit (the packed sums do not depend on arrival order)."""
+    N, K = 4096, 4096
+    layers, want, ys, graphs = [], [], [], []
+    for seed in (31, 32):
+        L = P.random_bcq_layer(N, K, 3, 128, seed=seed)
+        x = P.make_activation(K, seed=seed + 10).cuda()
+        t = (x, L["qweight"].cuda(), L["alpha"].cuda(), L["q_bias"].cuda())
+        y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+        ops.lutgemm_gemv(t[0], y, t[1], t[2], t[3], 3, 128)           # eager, on the current stream
+        layers.append(t)
+        want.append(y.clone())
+    torch.cuda.synchronize()
+    for t in layers:
+        cap = torch.cuda.Stream()                                      # never used before the capture
+        y = torch.zeros(1, 1, N, dtype=torch.float16, device="cuda")
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=cap):
+            y.zero_()
+            ops.lutgemm_gemv(t[0], y, t[1], t[2], t[3], 3, 128)
+        ys.append(y)
+        graphs.append(g)
+    run = [torch.cuda.Stream(), torch.cuda.Stream()]
+    for _ in range(200):
+        for g, s in zip(graphs, run):
+            with torch.cuda.stream(s):
+                g.replay()
+    torch.cuda.synchronize()
+    for y, w in zip(ys, want):
+        assert torch.equal(y, w)
+    assert ops.stream_status() == 0
+
+
 def test_wait_that_runs_out_is_reported_and_recoverable(ops):
     """Device-side failure handling without a GPU fault: under a test-only launch flag the producer of the pipelined
     binary-coded GEMV never issues its last stage (nothing is in flight for it), so the consumers' wait for that stage,

@@ -62,7 +62,7 @@ std::mutex g_mu;
 std::map<std::pair<int, cudaStream_t>, Workspace> g_ws;
 std::map<int, Workspace> g_ws_first;                       // first workspace of a device: capture fallback
 std::map<int, std::vector<Workspace>> g_ws_spare;          // set aside for streams first seen while capturing
-constexpr int kSpareWorkspaces = 4;
+constexpr int kSpareWorkspaces = 16;
 std::map<int, std::pair<cudaStream_t, std::pair<cudaEvent_t, cudaEvent_t>>> g_side;   // dummy_* side stream
 
 // A launch that gave up on a wait left its code in the workspace's error word: every later call on that stream

@@ -15,7 +15,7 @@
  *   - `stream` is a cudaStream_t passed as void*; work is enqueued, never synchronised;
  *   - pointers named *_dev must be device-accessible, *_host must be host memory;
  *   - the library keeps one small accumulator workspace per (device, stream).  The first compute call on a
- *     device allocates (its own and four spare ones) and therefore must not happen during stream capture.
+ *     device allocates (its own and sixteen spare ones, 2 MB each) and therefore must not happen during stream capture.
  *     A stream first seen while it is capturing takes a spare; when the spares are used up it shares the
  *     device's first workspace, and that graph must then not run concurrently with work on the owning stream.
  *     Calls that share a stream are ordered; calls on different streams use different workspaces.

@@ -12,7 +12,9 @@
 // table bytes at once - no shared-memory LUT, hence no bank conflicts.  Activations are staged in
 // shared memory once per CTA in the pair order the lookups produce.  Products are summed in half2
 // over 8 weights, then in fp32.
-// Generic path (4..8 bits, or K not a multiple of 128): one word per lane, LUT in shared memory.
+// Generic path (any width, any K multiple of 32): one word per lane, LUT in shared memory.
+// Both roles of this file are the fallback for shapes the pipelined kernel (gemv_anyprec_pipe.cuh) does not take
+// (K not a multiple of 128 or above 32768, or the pipeline switched off); common layers run there.
 #pragma once
 #include "common.cuh"
 
